@@ -1,0 +1,3 @@
+from .engine_config import EngineConfig, SelectiveCacheConfig
+from .model_config import ConfigError, YiConfig
+from .registry import ARCHITECTURES, Architecture, architecture_of, read_config, register_architecture, unregister_architecture

@@ -1,0 +1,219 @@
+"""The step function: one batch of (request, its next tokens) in, logits out.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere.
+Only the tokens it brings are run, as one batch, against the cache that earlier
+steps left; logits are made for the rows that are asked for.
+
+Reference counterpart: ``LMBackend._forward`` (DELTA/Engine/DELTA/backend.py:1641-1792)
+with its batch builders (1850-1936, 2040-2172) and ``Transformer.forward``
+(model.py:198-206).  The reference builds CSR page lists and calls a planning
+routine of its attention library every step; here the kernels read the block table
+rows directly, so the host work of a step is filling one staging buffer and one
+copy to the device.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from ..config.registry import architecture_of, read_config
+from ..kernels import ops
+from ..models.model import Model
+from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors
+from .context import StepContext
+
+
+@dataclass
+class RowInput:
+    """One request's share of a step: its next tokens, the position of the first of
+    them, and the places among them whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    start_pos: int
+    want: Sequence[int] = ()
+    selective: bool = False   # a decode token that DELTA's page selection applies to
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+def _require_cuda(device: torch.device) -> None:
+    if device.type != "cuda":
+        raise RuntimeError("delta_b200 runs on a CUDA device only; there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; delta_b200 has no CPU path")
+    torch.cuda.set_device(device)
+
+
+def _alloc_pinned(n: int) -> torch.Tensor:
+    return torch.empty(n, dtype=torch.int32, pin_memory=True)
+
+
+def _record_event():
+    ev = torch.cuda.Event()
+    ev.record()
+    return ev
+
+
+class ModelRunner:
+    """Owns the model, its weights, the cache manager and the step function."""
+
+    def __init__(self, model_dir=None, *, engine_config: Optional[EngineConfig] = None, config_json: Optional[dict] = None,
+                 seed: Optional[int] = None, device="cuda:0"):
+        self.cfg = engine_config or EngineConfig()
+        self.device = torch.device(device)
+        _require_cuda(self.device)
+        self.dtype = torch.bfloat16 if self.cfg.dtype == "bfloat16" else torch.float32
+        if model_dir is not None:
+            arch, self.model_config = read_config(model_dir)
+        elif config_json is not None:
+            arch = architecture_of(config_json)
+            self.model_config = arch.config_from_dict(config_json)
+        else:
+            raise ValueError("give a model folder, or config_json with a seed for random weights")
+        self.architecture = arch
+        self.spec = arch.build_spec(self.model_config, self.cfg)
+        self.model = Model(self.spec)
+        specs = self.model.tensor_specs()
+        if model_dir is not None:
+            tensors = load_tensors(model_dir, specs, self.dtype, self.device)
+        else:
+            tensors = random_tensors(specs, 0 if seed is None else seed, self.dtype, self.device)
+        self.model.bind(tensors)
+        self.cache = CacheManager(self.model.cache_specs(), self.model.state_specs(), max_slots=self.cfg.max_batch,
+                                  max_seq_len=self.cfg.max_seq_len, page_size=self.cfg.page_size,
+                                  num_pages=self.cfg.pool_pages, dtype=self.dtype, device=self.device,
+                                  shuffle_seed=self.cfg.shuffle_pages)
+        self.vocab_size = self.spec.vocab_size
+        self.err = ops.new_error_record(self.device)
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self._staging = []      # ring of (pinned buffer, event)
+        self._staging_next = 0
+        self.plain_products = False
+        self.plain_attention = False
+        self.capture: Optional[dict] = None
+        self.steps_run = 0
+
+    # ---- staging ---------------------------------------------------------------
+    def _pinned(self, n: int):
+        if len(self._staging) < 4:
+            self._staging.append([_alloc_pinned(max(n, 1 << 14)), None])
+        i = self._staging_next % len(self._staging)
+        self._staging_next += 1
+        buf, ev = self._staging[i]
+        if ev is not None:
+            ev.synchronize()
+        if buf.numel() < n:
+            buf = _alloc_pinned(n * 2)
+            self._staging[i][0] = buf
+        return i, buf
+
+    def build_context(self, rows: List[RowInput]) -> StepContext:
+        """Fills the staging buffer for these rows and copies it to the device."""
+        B = len(rows)
+        q_lens = [len(r.tokens) for r in rows]
+        T = sum(q_lens)
+        wants = []
+        q_start = []
+        off = 0
+        max_seq = 0
+        for r, n in zip(rows, q_lens):
+            if n < 1:
+                raise ValueError("a row of a step needs at least one token")
+            if not self.cache.is_live(r.slot):
+                raise ValueError(f"slot {r.slot} is not live")
+            for w in r.want:
+                if not (0 <= w < n):
+                    raise ValueError(f"wanted place {w} lies outside the row's {n} tokens")
+                wants.append(off + w)
+            q_start.append(off)
+            off += n
+            end = r.start_pos + n
+            max_seq = max(max_seq, end)
+            for g in self.cache.groups.values():
+                if int(g.num_logical[r.slot]) * g.page_size < end:
+                    raise ValueError(f"slot {r.slot} has no pages for {end} tokens; grow it before the step")
+        if len(set(r.slot for r in rows)) != B:
+            raise ValueError("a request appears twice in one step")
+        R = len(wants)
+        max_pages = max(1, _align((max_seq + self.cache.page_size - 1) // self.cache.page_size))
+        max_pages = min(max_pages, self.cache.max_pages_per_request) if self.cache.max_pages_per_request >= 1 else max_pages
+        names = list(self.cache.groups)
+        layout = {}
+        pos = 0
+        for key, n in (("tokens", T), ("tok_row", T), ("tok_pos", T), ("row_slot", B), ("row_flags", B), ("row_q_start", B),
+                       ("row_q_len", B), ("row_pos_start", B), ("logit_rows", R)):
+            layout[key] = (pos, n)
+            pos = _align(pos + n)
+        for g in names:
+            layout["bt:" + g] = (pos, B * max_pages)
+            pos = _align(pos + B * max_pages)
+        idx, pinned = self._pinned(pos)
+        host = pinned.numpy()
+
+        def put(key, values):
+            a, n = layout[key]
+            host[a:a + n] = values
+
+        if T:
+            put("tokens", np.concatenate([np.asarray(r.tokens, dtype=np.int32) for r in rows]))
+            put("tok_row", np.repeat(np.arange(B, dtype=np.int32), q_lens))
+            put("tok_pos", np.concatenate([np.arange(r.start_pos, r.start_pos + n, dtype=np.int32) for r, n in zip(rows, q_lens)]))
+        put("row_slot", [r.slot for r in rows])
+        put("row_flags", [1 if r.selective else 0 for r in rows])
+        put("row_q_start", q_start)
+        put("row_q_len", q_lens)
+        put("row_pos_start", [r.start_pos for r in rows])
+        put("logit_rows", wants)
+        slots = [r.slot for r in rows]
+        for g in names:
+            a, n = layout["bt:" + g]
+            host[a:a + n] = self.cache.groups[g].table[slots, :max_pages].reshape(-1)
+        dev = torch.empty(pos, dtype=torch.int32, device=self.device)
+        dev.copy_(pinned[:pos], non_blocking=True)
+        self._staging[idx][1] = _record_event()
+        sections = {k: dev[a:a + n] for k, (a, n) in layout.items() if not k.startswith("bt:")}
+        block_tables = {g: dev[layout["bt:" + g][0]:layout["bt:" + g][0] + B * max_pages].view(B, max_pages) for g in names}
+        info = dict(max_pages=max_pages, any_selective=any(r.selective for r in rows),
+                    decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens) if q_lens else 0, max_seq_len=max_seq,
+                    rows=rows, q_lens=q_lens, q_start=q_start, wants=wants)
+        return StepContext(device=self.device, dtype=self.dtype, cache=self.cache, sections=sections,
+                           block_tables=block_tables, host=info, err=self.err, scratch_pool=self._scratch,
+                           plain_products=self.plain_products, plain_attention=self.plain_attention, capture=self.capture)
+
+    # ---- the step ----------------------------------------------------------------
+    def step(self, rows: List[RowInput]) -> torch.Tensor:
+        """Runs one batch.  Pages for the new tokens must be held already
+        (``cache.grow``); afterwards the caller records the new lengths
+        (``cache.advance``).  Returns float32 logits [wanted places, vocab] on the
+        device, in the order of the rows and of their ``want`` lists."""
+        for r in rows:
+            if r.selective and len(r.tokens) != 1:
+                raise ValueError("page selection applies to single decode tokens only")
+        if not rows:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        ctx = self.build_context(rows)
+        logits = self.model.forward(ctx)
+        self.steps_run += 1
+        if self.cfg.check_kernel_errors:
+            ops.raise_if_error(self.err)
+        return logits
+
+    # ---- convenience used by replay and tests --------------------------------------
+    def run_rows(self, rows: List[RowInput]) -> torch.Tensor:
+        """grow, step, advance for every row."""
+        for r in rows:
+            self.cache.grow(r.slot, r.start_pos + len(r.tokens))
+        logits = self.step(rows)
+        for r in rows:
+            self.cache.advance(r.slot, r.start_pos + len(r.tokens))
+        return logits

@@ -1,0 +1,90 @@
+"""Loads the CUDA library and declares the C signature of every launcher.
+
+There is one code path: the hand-written kernels.  If the library cannot be
+built or loaded, or a tensor handed to a kernel is not on a CUDA device, the
+call raises; nothing falls back to the CPU or to library model code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+from .build import build
+
+_lock = threading.Lock()
+_lib = None
+
+P = C.c_void_p
+I = C.c_int
+F = C.c_float
+D = C.c_double
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or the launch failed."""
+
+
+class AttnParams(C.Structure):
+    """Mirror of ``DkAttnParams`` in csrc/attention_params.h."""
+    _fields_ = [
+        ("q", P), ("out", P), ("kv", P), ("block_table", P), ("tok_row", P), ("tok_pos", P),
+        ("row_slot", P), ("row_flags", P), ("row_q_start", P), ("row_q_len", P), ("row_pos_start", P),
+        ("sel_pages", P), ("sel_count", P), ("dump", P), ("lse", P), ("scratch", P), ("err", P),
+        ("T", I), ("rows", I), ("H", I), ("KV", I), ("hd", I), ("ps", I), ("max_pages", I), ("num_pages", I),
+        ("q_stride", I), ("window", I), ("sel_stride", I), ("dump_stride", I), ("dtype", I), ("splits", I),
+        ("scale", F), ("reserved", I),
+    ]
+
+
+_SIGNATURES = {
+    "dk_embedding": [P, P, P, I, I, I, I, P, P],
+    "dk_rms_norm": [P, P, P, P, P, I, I, F, I, I, I, P],
+    "dk_silu_mul": [P, P, I, I, I, P],
+    "dk_rope_append": [P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, P, P],
+    "dk_gather_rows_f32": [P, P, P, I, I, I, P],
+    "dk_gemm_nt_plain": [P, P, P, I, I, I, I, I, I, I, I, P],
+    "dk_attention_plain": [C.POINTER(AttnParams), P],
+    "dk_recent_pages": [P, P, P, P, P, P, I, I, I, D, P],
+    "dk_page_scores": [P, P, P, P, P, P, P, I, I, I, I, I, I, D, P],
+    "dk_select_pages": [P, P, P, P, P, P, P, I, I, I, I, I, F, D, P],
+    "dk_sample": [P, I, I, I, P, P, P, P, P, P, P],
+}
+
+
+def load():
+    """The loaded library (built at the first call)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = build()
+        lib = C.CDLL(str(path))
+        lib.dk_last_error.restype = C.c_char_p
+        lib.dk_last_error.argtypes = []
+        lib.dk_sizeof_attn_params.restype = I
+        if lib.dk_sizeof_attn_params() != C.sizeof(AttnParams):
+            raise KernelError(f"AttnParams is {C.sizeof(AttnParams)} bytes in Python and "
+                              f"{lib.dk_sizeof_attn_params()} in the library: the two declarations differ")
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = I
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def declare(name: str, argtypes: list) -> None:
+    """Adds a launcher's signature (used by kernel files that come later)."""
+    _SIGNATURES[name] = argtypes
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.restype = I
+        fn.argtypes = argtypes
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().dk_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{what}: {msg} (code {code})")

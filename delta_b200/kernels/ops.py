@@ -1,0 +1,207 @@
+"""Tensor-level entry points of the CUDA kernels.
+
+Each function checks that its tensors are CUDA tensors of the expected type and
+layout, and launches on torch's current stream.  Sizes that a kernel does not
+take are refused with an error by the launcher itself; nothing is computed on
+the CPU and no library model code is called.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import lib as _l
+from .lib import AttnParams, KernelError
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"the kernels take float32 and bfloat16, not {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor], name: str, dtype=None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on '{t.device}': the kernels run on CUDA tensors only and there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def new_error_record(device) -> torch.Tensor:
+    """Four ints the kernels write {code, a, b, c} into when they meet a bad index."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_ERR_TEXT = {1: "page id out of range (token {0}, logical page {1}, page id {2})",
+             2: "token id out of range (row {0}: id {1}, vocabulary {2})",
+             3: "position out of range (token {0}: position {1}, limit {2})"}
+
+
+def raise_if_error(err: torch.Tensor) -> None:
+    code, a, b, c = err.tolist()
+    if code != 0:
+        err.zero_()
+        raise KernelError("a kernel met a bad index and skipped it: " + _ERR_TEXT.get(code, "code {3}").format(a, b, c, code))
+
+
+# ---------------------------------------------------------------------------
+
+def embedding(tokens, table, out, err=None):
+    T, d = out.shape
+    _l.check(_l.load().dk_embedding(_ptr(tokens, "tokens", torch.int32), _ptr(table, "table"), _ptr(out, "out", table.dtype),
+                                    T, d, table.shape[0], dtype_code(table.dtype), _ptr(err, "err", torch.int32), _stream()),
+             "embedding")
+    return out
+
+
+def rms_norm(x, weight, eps, out, add=None, rows=None, cast_first=False):
+    """out[r] = rmsnorm(x[s]) * weight with s = rows[r] (or r); when ``add`` is
+    given, x[s] += add[s] first, in place.  ``rows`` must not name a row twice
+    together with ``add``."""
+    n_rows = out.shape[0]
+    d = x.shape[-1]
+    if add is not None and add.dtype != x.dtype:
+        raise KernelError("rms_norm: add and x differ in dtype")
+    _l.check(_l.load().dk_rms_norm(_ptr(x, "x"), _ptr(add, "add"), _ptr(weight, "weight"), _ptr(out, "out", x.dtype),
+                                   _ptr(rows, "rows", torch.int32), n_rows, d, float(eps), dtype_code(x.dtype),
+                                   dtype_code(weight.dtype), int(bool(cast_first)), _stream()), "rms_norm")
+    return out
+
+
+def silu_mul(gate_up, out):
+    T, I2 = gate_up.shape
+    _l.check(_l.load().dk_silu_mul(_ptr(gate_up, "gate_up"), _ptr(out, "out", gate_up.dtype), T, I2 // 2,
+                                   dtype_code(gate_up.dtype), _stream()), "silu_mul")
+    return out
+
+
+def rope_append(qkv, tok_pos, tok_row, block_table, kv, table, H, KV, hd, ps, interleaved, err=None):
+    """Rotates q and k inside ``qkv`` [T, (H+2KV)*hd] and appends k, v to the pages
+    of ``kv`` [pages, 2, KV, ps, hd].  ``table`` [positions, hd/2, 2] float holds
+    cos and sin; None leaves q and k unrotated.  ``kv`` None appends nothing."""
+    T = qkv.shape[0]
+    if qkv.shape[1] != (H + 2 * KV) * hd:
+        raise KernelError(f"rope_append: qkv has width {qkv.shape[1]}, expected {(H + 2 * KV) * hd}")
+    if kv is not None and (tuple(kv.shape[1:]) != (2, KV, ps, hd) or kv.dtype != qkv.dtype):
+        raise KernelError(f"rope_append: cache has shape {tuple(kv.shape)} / {kv.dtype}, expected [pages, 2, {KV}, {ps}, {hd}] of {qkv.dtype}")
+    if table is not None and (table.dim() != 3 or table.shape[1] != hd // 2 or table.shape[2] != 2):
+        raise KernelError(f"rope_append: table has shape {tuple(table.shape)}, expected [positions, {hd // 2}, 2]")
+    _l.check(_l.load().dk_rope_append(
+        _ptr(qkv, "qkv"), _ptr(tok_pos, "tok_pos", torch.int32), _ptr(tok_row, "tok_row", torch.int32),
+        _ptr(block_table, "block_table", torch.int32), block_table.shape[1] if block_table is not None else 0,
+        _ptr(kv, "kv"), kv.shape[0] if kv is not None else 0, _ptr(table, "table", torch.float32),
+        table.shape[0] if table is not None else 0, T, H, KV, hd, ps, int(bool(interleaved)), dtype_code(qkv.dtype),
+        _ptr(err, "err", torch.int32), _stream()), "rope_append")
+
+
+def gather_rows_f32(x, rows, out):
+    _l.check(_l.load().dk_gather_rows_f32(_ptr(x, "x"), _ptr(rows, "rows", torch.int32), _ptr(out, "out", torch.float32),
+                                          out.shape[0], x.shape[1], dtype_code(x.dtype), _stream()), "gather_rows")
+    return out
+
+
+def gemm_nt_plain(a, w, out):
+    """out[M,N] = a[M,K] @ w[N,K]^T on the FMA units with float accumulation."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != w.dtype:
+        raise KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} or dtypes do not fit")
+    _l.check(_l.load().dk_gemm_nt_plain(_ptr(a, "a"), _ptr(w, "w"), _ptr(out, "out"), M, N, K, K, K, N,
+                                        dtype_code(a.dtype), dtype_code(out.dtype), _stream()), "gemm_nt_plain")
+    return out
+
+
+def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, KV, hd, ps, scale, row_slot=None,
+                     row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None, sel_pages=None,
+                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0) -> AttnParams:
+    p = AttnParams()
+    i32 = torch.int32
+    p.q = _ptr(q, "q")
+    p.out = _ptr(out, "out", q.dtype)
+    p.kv = _ptr(kv, "kv", q.dtype)
+    if tuple(kv.shape[1:]) != (2, KV, ps, hd):
+        raise KernelError(f"attention: cache has shape {tuple(kv.shape)}, expected [pages, 2, {KV}, {ps}, {hd}]")
+    p.block_table = _ptr(block_table, "block_table", i32)
+    p.tok_row = _ptr(tok_row, "tok_row", i32)
+    p.tok_pos = _ptr(tok_pos, "tok_pos", i32)
+    p.row_slot = _ptr(row_slot, "row_slot", i32)
+    p.row_flags = _ptr(row_flags, "row_flags", i32)
+    p.row_q_start = _ptr(row_q_start, "row_q_start", i32)
+    p.row_q_len = _ptr(row_q_len, "row_q_len", i32)
+    p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
+    p.sel_pages = _ptr(sel_pages, "sel_pages", i32)
+    p.sel_count = _ptr(sel_count, "sel_count", i32)
+    p.dump = _ptr(dump, "dump", torch.float32)
+    p.lse = _ptr(lse, "lse", torch.float32)
+    p.scratch = _ptr(scratch, "scratch")
+    p.err = _ptr(err, "err", i32)
+    p.T = tok_row.shape[0]
+    p.rows = block_table.shape[0]
+    p.H, p.KV, p.hd, p.ps = H, KV, hd, ps
+    p.max_pages = block_table.shape[1]
+    p.num_pages = kv.shape[0]
+    p.q_stride = q_stride
+    p.window = int(window or 0)
+    p.sel_stride = sel_pages.shape[1] if sel_pages is not None else 0
+    p.dump_stride = dump.shape[-1] if dump is not None else 0
+    p.dtype = dtype_code(q.dtype)
+    p.splits = splits
+    p.scale = float(scale)
+    return p
+
+
+def attention_plain(params: AttnParams):
+    _l.check(_l.load().dk_attention_plain(C.byref(params), _stream()), "attention_plain")
+
+
+def recent_pages(row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, ps, ratio):
+    i32 = torch.int32
+    _l.check(_l.load().dk_recent_pages(_ptr(row_slot, "row_slot", i32), _ptr(row_flags, "row_flags", i32),
+                                       _ptr(row_pos_start, "row_pos_start", i32), _ptr(row_q_len, "row_q_len", i32),
+                                       _ptr(sel_pages, "sel_pages", i32), _ptr(sel_count, "sel_count", i32),
+                                       row_slot.shape[0], sel_pages.shape[1], ps, float(ratio), _stream()), "recent_pages")
+
+
+def page_scores(dump, lse, row_flags, row_q_start, row_pos_start, row_q_len, scores, ps, k, ratio):
+    rows, H, stride = dump.shape
+    i32 = torch.int32
+    _l.check(_l.load().dk_page_scores(_ptr(dump, "dump", torch.float32), _ptr(lse, "lse", torch.float32),
+                                      _ptr(row_flags, "row_flags", i32), _ptr(row_q_start, "row_q_start", i32),
+                                      _ptr(row_pos_start, "row_pos_start", i32), _ptr(row_q_len, "row_q_len", i32),
+                                      _ptr(scores, "scores", torch.float32), rows, H, ps, stride, scores.shape[1], k,
+                                      float(ratio), _stream()), "page_scores")
+
+
+def select_pages(scores, row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, keep_last, ps, bias, ratio):
+    i32 = torch.int32
+    _l.check(_l.load().dk_select_pages(_ptr(scores, "scores", torch.float32), _ptr(row_slot, "row_slot", i32),
+                                       _ptr(row_flags, "row_flags", i32), _ptr(row_pos_start, "row_pos_start", i32),
+                                       _ptr(row_q_len, "row_q_len", i32), _ptr(sel_pages, "sel_pages", i32),
+                                       _ptr(sel_count, "sel_count", i32), scores.shape[0], scores.shape[1],
+                                       sel_pages.shape[1], keep_last, ps, float(bias), float(ratio), _stream()), "select_pages")
+
+
+def sample(logits, out, temperature=None, top_p=None, seeds=None, positions=None, out_copy=None):
+    """One token per row of float ``logits`` [R, V]: greedy where temperature is 0
+    (or not given), else a draw from softmax(logits / temperature)."""
+    R, V = logits.shape
+    _l.check(_l.load().dk_sample(_ptr(logits, "logits", torch.float32), logits.stride(0) if R else V, R, V,
+                                 _ptr(temperature, "temperature", torch.float32), _ptr(top_p, "top_p", torch.float32),
+                                 _ptr(seeds, "seeds", torch.int64), _ptr(positions, "positions", torch.int32),
+                                 _ptr(out, "out", torch.int32), _ptr(out_copy, "out_copy", torch.int32), _stream()), "sample")
+    return out

@@ -1,0 +1,121 @@
+"""Grouped-query attention over the paged cache, with DELTA's three layer roles.
+
+One projection gives q, k and v (rows of q_proj, k_proj, v_proj stacked, as the
+reference's ``load_hook`` does, DELTA/Engine/DELTA/model.py:394-399); q and k
+get their position encoding, k and v are appended to the layer's pages, and
+every new token attends causally to the keys of its request
+(model.py:437-492; backend.py:461-484).
+
+``role`` (model.py:177-194):
+  "full"     reads every key (or the last ``window`` of them);
+  "planner"  as "full", and for decode rows it also scores the request's pages
+             from this layer's attention and chooses ``subset_cache_size`` of them
+             (backend.py:518-581, 787-853, 887-904; page_selector_v2.py:113-150);
+  "subset"   decode rows read only the chosen pages (backend.py:486-516); before a
+             planner has run in a step these are the most recent pages
+             (backend.py:1871-1873).
+Rows of a prompt always read everything.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from . import linear
+from .base import MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, StateSpec, TensorSpec
+
+SELECTED_PAGES = "delta.selected_pages"
+SELECTED_COUNT = "delta.selected_count"
+
+
+@MIXERS.register("gqa_attention")
+class GQAAttention(Mixer):
+    def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int,
+                 position: Optional[PartSpec] = None, window: Optional[int] = None, role: str = "full",
+                 subset_cache_size: int = 0, keep_last: int = 1, compression_ratio: float = 1.0,
+                 position_bias: float = 1e-7, scale: Optional[float] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads are no multiple of {kv_heads} key-value heads")
+        if role not in ("full", "planner", "subset"):
+            raise ValueError(f"unknown attention role '{role}'")
+        if role != "full" and subset_cache_size < 1:
+            raise ValueError("a planner or subset layer needs subset_cache_size >= 1")
+        if role != "full" and window:
+            raise ValueError("a windowed layer reads a bounded number of keys already; it takes no page selection")
+        self.prefix = prefix
+        self.width, self.heads, self.kv_heads, self.head_dim = int(width), int(heads), int(kv_heads), int(head_dim)
+        self.window = int(window) if window else None
+        self.role = role
+        self.k = int(subset_cache_size)
+        self.keep_last = int(keep_last)
+        self.ratio = float(compression_ratio)
+        self.bias = float(position_bias)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = position.build(POSITION_ENCODINGS) if position is not None else None
+        self.w_qkv = None
+        self.w_o = None
+
+    # ---- what it needs ---------------------------------------------------
+    def tensor_specs(self):
+        p, d, hd = self.prefix, self.width, self.head_dim
+        return [TensorSpec(p + "q_proj.weight", (self.heads * hd, d)), TensorSpec(p + "k_proj.weight", (self.kv_heads * hd, d)),
+                TensorSpec(p + "v_proj.weight", (self.kv_heads * hd, d)), TensorSpec(p + "o_proj.weight", (d, self.heads * hd))]
+
+    def bind(self, tensors):
+        p = self.prefix
+        self.w_qkv = torch.cat([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]],
+                               dim=0).contiguous()
+        self.w_o = tensors[p + "o_proj.weight"]
+
+    def cache_spec(self):
+        return CacheSpec(self.kv_heads, self.head_dim, self.window)
+
+    def state_specs(self):
+        if self.role == "full":
+            return {}
+        return {SELECTED_PAGES: StateSpec((self.k,), torch.int32, 0), SELECTED_COUNT: StateSpec((), torch.int32, -1)}
+
+    # ---- a step ------------------------------------------------------------
+    def begin_step(self, ctx):
+        if self.role == "full" or not ctx.any_selective or not ctx.once("delta.recent_pages"):
+            return
+        ops.recent_pages(ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
+                         ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), ctx.page_size, self.ratio)
+
+    def forward(self, ctx, x, cache):
+        H, KV, hd = self.heads, self.kv_heads, self.head_dim
+        T = x.shape[0]
+        qkv = linear.linear(ctx, x, self.w_qkv)
+        table = self.position.table(x.device) if self.position is not None else None
+        interleaved = bool(getattr(self.position, "interleaved", False))
+        ops.rope_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.kv if cache.writes else None, table,
+                        H, KV, hd, cache.page_size, interleaved, err=ctx.err)
+        out = torch.empty((T, H * hd), dtype=x.dtype, device=x.device)
+        selective = self.role != "full" and ctx.any_selective
+        dump = lse = None
+        if self.role == "planner" and selective:
+            dump = ctx.scratch("delta.dump", (ctx.num_rows, H, ctx.max_pages * cache.page_size), torch.float32)
+            lse = ctx.scratch("delta.lse", (T, H), torch.float32)
+        params = ops.make_attn_params(
+            q=qkv, q_stride=qkv.shape[1], out=out, kv=cache.kv, block_table=cache.block_table, tok_row=ctx.tok_row,
+            tok_pos=ctx.tok_pos, H=H, KV=KV, hd=hd, ps=cache.page_size, scale=self.scale, row_slot=ctx.row_slot,
+            row_flags=ctx.row_flags, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_pos_start=ctx.row_pos_start,
+            sel_pages=ctx.state(SELECTED_PAGES) if (self.role == "subset" and selective) else None,
+            sel_count=ctx.state(SELECTED_COUNT) if (self.role == "subset" and selective) else None,
+            dump=dump, lse=lse, err=ctx.err, window=self.window or 0)
+        ctx.attention(params)
+        if self.role == "planner" and selective:
+            scores = ctx.scratch("delta.page_scores", (ctx.num_rows, ctx.max_pages), torch.float32)
+            ops.page_scores(dump, lse, ctx.row_flags, ctx.row_q_start, ctx.row_pos_start, ctx.row_q_len, scores,
+                            cache.page_size, self.k, self.ratio)
+            ops.select_pages(scores, ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
+                             ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), self.keep_last, cache.page_size,
+                             self.bias, self.ratio)
+            if ctx.capture is not None:
+                ctx.capture.setdefault("page_scores", []).append((self.prefix, scores.clone()))
+                ctx.capture.setdefault("selected", []).append(
+                    (self.prefix, ctx.state(SELECTED_PAGES).clone(), ctx.state(SELECTED_COUNT).clone()))
+        return linear.linear(ctx, out, self.w_o)
