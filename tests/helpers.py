@@ -103,3 +103,51 @@ def mixed(lengths, prompt_lens, seed=0, max_live=4, portion_sizes=(5, 2, 11, 3, 
             steps.append(step)
             ends.append(done)
     return steps, ends
+
+
+# ---- running a schedule through the engine's step function -----------------------
+
+def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, selective=False):
+    """Feeds the schedule through ``runner`` (a ModelRunner) and returns
+    {(request, position): logits row (CPU float32)}.  Logits are asked for at every
+    token.  With ``selective`` the single tokens at or after a request's prompt
+    length are decode tokens that page selection applies to."""
+    from delta_b200.engine.step import RowInput
+    slots = {}
+    out = {}
+    for k, step in enumerate(steps):
+        rows, keys = [], []
+        for (i, start, count) in step:
+            if i not in slots:
+                slots[i] = runner.cache.acquire_slot()
+            sel = bool(selective and count == 1 and prompt_lens is not None and start >= prompt_lens[i])
+            rows.append(RowInput(slots[i], token_lists[i][start:start + count], start, list(range(count)), selective=sel))
+            keys.extend((i, start + j) for j in range(count))
+        logits = runner.run_rows(rows).float().cpu()
+        assert logits.shape[0] == len(keys)
+        for key, row in zip(keys, logits):
+            assert key not in out, f"position {key} was fed twice"
+            out[key] = row
+        for i in (ends[k] if ends is not None else []):
+            runner.cache.release_slot(slots.pop(i))
+        runner.cache.check()
+    for i in list(slots):
+        runner.cache.release_slot(slots.pop(i))
+    runner.cache.check()
+    return out
+
+
+def stack_positions(results, request, length):
+    return torch.stack([results[(request, p)] for p in range(length)])
+
+
+def peak_pages(steps, ends, page_size):
+    """Most pages held at any time when the schedule runs (no windows counted)."""
+    held, peak = {}, 0
+    for k, step in enumerate(steps):
+        for (i, start, count) in step:
+            held[i] = (start + count + page_size - 1) // page_size
+        peak = max(peak, sum(held.values()))
+        for i in (ends[k] if ends is not None else []):
+            held.pop(i, None)
+    return peak
