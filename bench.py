@@ -1,0 +1,245 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the delta_b200 engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L]
+
+Default run: the layer sizes of Yi-6B (32 layers, hidden 4096, 32 heads over 4
+key-value heads of 128, intermediate 11008, vocabulary 64000), random bfloat16
+weights, 8 requests decoding at a context of 4096 tokens.  One step is one decode
+step.  It prints ONE JSON line:
+
+  value      decoded tokens per second, device time of the K timed steps (model step
+             and sampling, measured with CUDA events around each step)
+  e2e        the same through the Python entry point (LMBackend.step): every step
+             copies its inputs from pinned host memory and reads the new tokens back
+  prefill    one prompt of 2,048 tokens in one step; frac = flops / time / peak
+  roofline   bytes a decode step has to read (every weight once, and the cache of the
+             live requests) / its time, against the copy bandwidth
+  points     decode tokens per second at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else
+from the fallback figures of an earlier measurement on this pool.  The engine runs on
+one GPU only: for --gpus above 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+YI_6B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=4096, num_hidden_layers=32,
+             num_attention_heads=32, num_key_value_heads=4, intermediate_size=11008, vocab_size=64000,
+             rope_theta=5000000.0, rms_norm_eps=1e-5, max_position_embeddings=4096, hidden_act="silu",
+             tie_word_embeddings=False, torch_dtype="bfloat16")
+FULL_LAYERS = 32
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            out = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+                       source="measured")
+            return out
+        except Exception:  # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return dict(sm_mhz=mhz[len(mhz) // 2] if mhz else None, sm_max_mhz=mx, reasons=sorted(reasons), samples=len(mhz))
+
+
+def model_numbers(cfg: dict, layers: int):
+    d, H, KV = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = cfg.get("head_dim") or d // H
+    I, V = cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (H + 2 * KV) * hd * d + H * hd * d + 3 * I * d
+    weight_bytes = 2 * (layers * (per_layer + 2 * d) + V * d + d)
+    kv_bytes_per_token = layers * 2 * KV * hd * 2
+
+    def prefill_flops(T):
+        gemm = 2 * T * layers * per_layer + 2 * V * d  # logits for one row
+        attn = layers * 4 * hd * H * (T * (T + 1) // 2)
+        return gemm + attn
+    return weight_bytes, kv_bytes_per_token, prefill_flops
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "hoenza/DELTA has no setup.py or pyproject.toml (pip: 'not installable'), and its attention "
+                          "library pins kernels that have no sm_100 build"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported (single-GPU engine tier)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from delta_b200.engine import LMBackend
+    from delta_b200.kernels import ops
+
+    cfg = dict(YI_6B, num_hidden_layers=args.layers)
+    pk = peaks()
+    weight_bytes, kv_per_tok, prefill_flops = model_numbers(cfg, args.layers)
+    ctx_len = args.context
+    max_b = 64 if not args.skip_points else args.batch
+    eng = LMBackend(dtype=torch.bfloat16, device="cuda:0", cuda_graph_decode=not args.no_graph)
+    eng.load_model(config_json=cfg, seed=0)
+    eng.setup_caches(max_batch_size=max(max_b, args.batch), max_seq_length=ctx_len, page_size=16, max_tokens_per_step=2048)
+    gen = torch.Generator().manual_seed(1)
+
+    def fresh_prompts(n, length):
+        return [torch.randint(0, cfg["vocab_size"], (length,), generator=gen).tolist() for _ in range(n)]
+
+    def run_decode(batch, steps, warmup, through_api_wall=False):
+        """Prefills ``batch`` requests so that the timed decode steps end at the context
+        length, then times ``steps`` decode steps.  Returns (device ms per step, end-to-end
+        ms per step, launches per step, bytes in, bytes out, mean context)."""
+        total_new = warmup + steps + 1
+        plen = ctx_len - total_new
+        sch = eng.scheduler
+        sch.decode_while_prefill = False
+        eng.add_requests(fresh_prompts(batch, plen), [ctx_len] * batch, [])
+        while sch.waiting or any(not r.output for r in sch.running):
+            eng.step()
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        l0 = ops.launch_count()
+        dev_ms = 0.0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        eng.record_timings = True
+        eng.step_timings.clear()
+        e0.record()
+        for _ in range(steps):
+            eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        eng.record_timings = False
+        e2e_ms = e0.elapsed_time(e1) / steps
+        dev_ms = sum(s["model_forward_ms"] + s["postprocess_ms"] for s in eng.step_timings) / steps
+        launches = (ops.launch_count() - l0) / steps
+        mean_ctx = plen + warmup + steps / 2
+        h2d = eng.runner.last_staging_bytes
+        sch.abort_all("bench")
+        return dev_ms, e2e_ms, launches, h2d, 4 * batch, mean_ctx
+
+    # ---- prefill of 2,048 tokens ------------------------------------------------
+    T = 2048
+    pre_ms = []
+    for i in range(3):
+        eng.add_requests(fresh_prompts(1, T), [T + 1], [])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+        eng.scheduler.abort_all("bench")
+    pre = min(pre_ms[1:])
+    prefill = dict(value=T / (pre / 1e3), tokens=T, ms=pre, frac=prefill_flops(T) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12))
+
+    # ---- the headline: decode at the default batch --------------------------------
+    clocks = ClockSampler()
+    clocks.start()
+    dev_ms, e2e_ms, launches, h2d, d2h, mean_ctx = run_decode(args.batch, args.steps, args.warmup)
+    clk = clocks.stop()
+    value = args.batch / (dev_ms / 1e3)
+    bytes_step = weight_bytes + args.batch * mean_ctx * kv_per_tok
+    achieved = bytes_step / (dev_ms / 1e3) / 1e9
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            d_ms, _, _, _, _, _ = run_decode(b, max(16, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = b / (d_ms / 1e3)
+
+    out = {
+        "metric": "decode tok/s (Yi-6B shape, bf16, batch 8, context 4096)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+        "config": {"model": "Yi-6B shape", "layers": args.layers, "layers_of_named_config": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": ctx_len, "page_size": 16, "parallelism": "single GPU",
+                   "cuda_graph_decode": not args.no_graph, "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
+                   "peaks": pk["source"]},
+        "e2e": {"value": args.batch / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(round(launches * args.steps)),
+        "clocks": clk,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

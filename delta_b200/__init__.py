@@ -4,3 +4,11 @@ from . import models  # noqa: F401  (registers the architectures)
 from .config import EngineConfig, SelectiveCacheConfig, YiConfig
 
 __all__ = ["EngineConfig", "SelectiveCacheConfig", "YiConfig"]
+
+
+def __getattr__(name):
+    # the engine pulls in the CUDA library; import it on first use
+    if name in ("LMBackend", "ModelRunner", "RowInput"):
+        from . import engine
+        return getattr(engine, name)
+    raise AttributeError(name)

@@ -1,0 +1,181 @@
+"""The Python entry point, in the manner of the reference's ``LMBackend``.
+
+The reference is used like this (tests/reasoni.py:320-342, 449-455):
+
+    e = LMBackend(dtype=torch.bfloat16, device="cuda:0", cuda_graph_decode=...)
+    e.load_model(path)
+    e.model.config.enable_selective_cache = ...   # and full_cache_layers, subset_cache_size, ...
+    e.setup_caches(max_batch_size=B, max_seq_length=max_len)
+    e.add_requests(list_of_id_tensors, max_lengths, eot_token_ids)
+    results = e.run_scheduler_loop()
+
+The same calls work here.  ``load_model`` takes a model folder (config.json and
+safetensors) instead of a converted ``model.pth``; the selective-cache options are
+arguments of ``setup_caches`` (or attributes of ``options`` set before it).
+Results have the reference's keys (scheduler.py:166-182) plus the generated ids.
+"""
+from __future__ import annotations
+
+import time
+from types import SimpleNamespace
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..config.engine_config import EngineConfig, SelectiveCacheConfig
+from ..sampling.sampler import SamplingParams, sample
+from .scheduler import PlannedRow, Scheduler
+from .step import ModelRunner, RowInput
+
+
+class LMBackend:
+    def __init__(self, dtype=torch.bfloat16, device: str = "cuda:0", cuda_graph_decode: bool = False, **unused):
+        if dtype in (torch.bfloat16, "bfloat16", "bf16"):
+            self.dtype = "bfloat16"
+        elif dtype in (torch.float32, "float32", "fp32"):
+            self.dtype = "float32"
+        else:
+            raise ValueError(f"dtype {dtype} is not supported: bfloat16 or float32")
+        self.device = device
+        self.cuda_graph_decode = bool(cuda_graph_decode)
+        # the reference's scripts set these on model.config; here they are plain options
+        self.options = SimpleNamespace(enable_selective_cache=False, full_cache_layers=None, subset_cache_size=1024,
+                                       compression_ratio=1.0, L=8)
+        self._model_dir = None
+        self._config_json = None
+        self._seed = None
+        self.runner: Optional[ModelRunner] = None
+        self.scheduler: Optional[Scheduler] = None
+        self.tokenizer = None
+        self.step_timings: List[dict] = []
+        self.throughput_mode = False
+        self.record_timings = False
+
+    # ---- set-up -------------------------------------------------------------
+    def load_model(self, model_dir=None, *, config_json: Optional[dict] = None, seed: Optional[int] = None, **unused):
+        """Names the model: a folder, or a config.json dict with a seed for random weights.
+        The weights are read when the caches are set up."""
+        if model_dir is None and config_json is None:
+            raise ValueError("give a model folder or config_json with a seed")
+        self._model_dir, self._config_json, self._seed = model_dir, config_json, seed
+
+    def set_tokenizer(self, tokenizer):
+        self.tokenizer = tokenizer
+
+    def setup_caches(self, max_batch_size: int = 1, max_seq_length: int = 2048, *, page_size: int = 16,
+                     num_pages: Optional[int] = None, max_tokens_per_step: int = 2048,
+                     enable_selective_cache: Optional[bool] = None, full_cache_layers=None,
+                     subset_cache_size: Optional[int] = None, compression_ratio: Optional[float] = None,
+                     L: Optional[int] = None, check_kernel_errors: bool = False, rope_interleaved: bool = False):
+        o = self.options
+        if enable_selective_cache is not None:
+            o.enable_selective_cache = enable_selective_cache
+        if full_cache_layers is not None:
+            o.full_cache_layers = full_cache_layers
+        if subset_cache_size is not None:
+            o.subset_cache_size = subset_cache_size
+        if compression_ratio is not None:
+            o.compression_ratio = compression_ratio
+        if L is not None:
+            o.L = L
+        selective = None
+        if o.enable_selective_cache and o.full_cache_layers:
+            selective = SelectiveCacheConfig(full_cache_layers=tuple(o.full_cache_layers), subset_cache_size=o.subset_cache_size,
+                                             compression_ratio=float(o.compression_ratio), L=o.L)
+        cfg = EngineConfig(max_batch=max_batch_size, max_seq_len=max_seq_length, page_size=page_size, num_pages=num_pages,
+                           dtype=self.dtype, max_tokens_per_step=max_tokens_per_step,
+                           cuda_graph_decode=self.cuda_graph_decode, selective=selective,
+                           check_kernel_errors=check_kernel_errors, rope_interleaved=rope_interleaved)
+        self.engine_config = cfg
+        self.runner = ModelRunner(self._model_dir, engine_config=cfg, config_json=self._config_json, seed=self._seed,
+                                  device=self.device)
+        self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch_size, max_tokens_per_step=max_tokens_per_step,
+                                   selective=selective is not None)
+
+    # ---- requests ---------------------------------------------------------------
+    def add_requests(self, input_ids_list, max_lengths, eot_token_ids: Sequence[int] = (), *, temperature=0.0, top_p=1.0,
+                     seed: int = 0, max_new_tokens: Optional[int] = None):
+        """One request per prompt (lists or 1-D tensors of token ids).  ``max_lengths`` is a
+        number or a list: the most tokens a request may reach, prompt included."""
+        out = []
+        for i, ids in enumerate(input_ids_list):
+            ids = ids.tolist() if hasattr(ids, "tolist") else list(ids)
+            ml = max_lengths[i] if isinstance(max_lengths, (list, tuple)) else max_lengths
+            t = temperature[i] if isinstance(temperature, (list, tuple)) else temperature
+            sp = SamplingParams(temperature=float(t), top_p=float(top_p), seed=int(seed) + len(self.scheduler.requests))
+            out.append(self.scheduler.add_request(ids, ml, eot_token_ids, sp, max_new_tokens))
+        return out
+
+    # ---- the loop -----------------------------------------------------------------
+    def step(self) -> List:
+        """One scheduler step: plan, run, sample, book.  Returns the requests that finished."""
+        sch, runner = self.scheduler, self.runner
+        t0 = time.perf_counter()
+        plan = sch.schedule()
+        if not plan:
+            if sch.has_work() and not sch.running:
+                # nothing runs and the head of the queue cannot be admitted: it never will be
+                r = sch.waiting.pop(0)
+                sch._fail(r, "cannot be admitted: not enough cache pages")
+                return [r]
+            return []
+        rows = []
+        samp, positions = [], []
+        for x in plan:
+            r = x.request
+            toks = r.tokens[x.start:x.start + x.count]
+            rows.append(RowInput(r.slot, toks, x.start, [x.count - 1] if x.samples else [],
+                                 selective=bool(sch.selective and x.decode)))
+            if x.samples:
+                samp.append(r.sampling)
+                positions.append(x.start + x.count)
+        ev = None
+        if self.record_timings:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
+        logits = runner.step(rows)
+        if ev:
+            ev[1].record()
+        new_tokens = sample(logits, samp, positions).tolist() if samp else []
+        if ev:
+            ev[2].record()
+            torch.cuda.synchronize()
+            self.step_timings.append(dict(plan_ms=0.0, model_forward_ms=ev[0].elapsed_time(ev[1]),
+                                          postprocess_ms=ev[1].elapsed_time(ev[2]),
+                                          step_total_ms=(time.perf_counter() - t0) * 1e3,
+                                          active_bsz=len(rows), tokens=sum(x.count for x in plan),
+                                          total_pages=sum(runner.cache.pages_in_use().values())))
+        return sch.complete(plan, new_tokens)
+
+    def run_scheduler_loop(self) -> List[dict]:
+        """Runs until every request is finished (or, in throughput mode, until the first one
+        is: reference backend.py:1501-1505) and returns the per-request results."""
+        sch = self.scheduler
+        self.loop_start = time.perf_counter()
+        while sch.has_work():
+            finished = self.step()
+            if self.throughput_mode and finished:
+                sch.abort_all("throughput mode: first request finished")
+                break
+        torch.cuda.synchronize()
+        self.loop_time = time.perf_counter() - self.loop_start
+        return self.get_detailed_results()
+
+    def get_detailed_results(self) -> List[dict]:
+        res = self.scheduler.results()
+        if self.tokenizer is not None:
+            for r in res:
+                req = self.scheduler.requests[r["request_id"]]
+                r["input_text"] = self.tokenizer.decode(req.prompt, skip_special_tokens=True)
+                r["output_text"] = self.tokenizer.decode(req.output, skip_special_tokens=True)
+        return res
+
+    # ---- convenience -----------------------------------------------------------------
+    def generate(self, prompts, max_new_tokens: int, *, temperature=0.0, top_p=1.0, seed=0, stop_ids=()) -> List[List[int]]:
+        """Token ids in, generated token ids out (host lists)."""
+        first = len(self.scheduler.requests)
+        limit = self.engine_config.max_seq_len
+        self.add_requests(prompts, [min(limit, len(p) + max_new_tokens) for p in prompts], stop_ids, temperature=temperature,
+                          top_p=top_p, seed=seed, max_new_tokens=max_new_tokens)
+        self.run_scheduler_loop()
+        return [list(r.output) for r in self.scheduler.requests[first:]]

@@ -102,6 +102,7 @@ class ModelRunner:
         self.plain_attention = False
         self.capture: Optional[dict] = None
         self.steps_run = 0
+        self.last_staging_bytes = 0
 
     # ---- staging ---------------------------------------------------------------
     def _pinned(self, n: int):
@@ -178,6 +179,7 @@ class ModelRunner:
         for g in names:
             a, n = layout["bt:" + g]
             host[a:a + n] = self.cache.groups[g].table[slots, :max_pages].reshape(-1)
+        self.last_staging_bytes = pos * 4
         dev = torch.empty(pos, dtype=torch.int32, device=self.device)
         dev.copy_(pinned[:pos], non_blocking=True)
         self._staging[idx][1] = _record_event()

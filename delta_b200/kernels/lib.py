@@ -84,7 +84,12 @@ def declare(name: str, argtypes: list) -> None:
         fn.argtypes = argtypes
 
 
-def check(code: int, what: str) -> None:
+LAUNCHES = [0]
+
+
+def check(code: int, what: str, kernels: int = 1) -> None:
+    """Raises when a launcher returned an error; counts the kernels it launched."""
+    LAUNCHES[0] += kernels
     if code != 0:
         msg = load().dk_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what}: {msg} (code {code})")

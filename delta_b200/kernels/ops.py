@@ -42,6 +42,15 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+def launch_count() -> int:
+    """Kernels launched through this module so far (library products included)."""
+    return _l.LAUNCHES[0]
+
+
+def count_launch(n: int = 1) -> None:
+    _l.LAUNCHES[0] += n
+
+
 def new_error_record(device) -> torch.Tensor:
     """Four ints the kernels write {code, a, b, c} into when they meet a bad index."""
     return torch.zeros(4, dtype=torch.int32, device=device)

@@ -240,10 +240,10 @@ class Selective:
 
     def role(self, layer: int, n_layers: int) -> str:
         """full / planner / subset   (DELTA/Engine/DELTA/model.py:177-194)."""
-        if not self.full_layers or layer in self.full_layers:
+        if not self.full_layers:
+            return "full"
+        if layer in self.full_layers:
             nxt_full = True if layer + 1 >= n_layers else (layer + 1) in self.full_layers
-            if not self.full_layers:
-                nxt_full = True
             return "full" if nxt_full else "planner"
         return "subset"
 
@@ -313,7 +313,8 @@ class PlainYi:
         caches = {}
         self.last_selection = {}
         for (i, cache_id, writes) in c.plan:
-            role = selective.role(i, c.layers) if selective else "full"
+            # a layer with a window reads a bounded number of keys already and takes no page selection
+            role = selective.role(i, c.layers) if (selective and c.windows[i] is None) else "full"
             mask = causal_mask(T, c.windows[i])
             if role == "subset":
                 for p in range(T):

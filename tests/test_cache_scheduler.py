@@ -1,0 +1,233 @@
+"""The cache manager's bookkeeping and the scheduler's decisions (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from delta_b200.cache import CacheManager, OutOfPages, PagePool
+from delta_b200.engine.scheduler import FAILED, FINISHED, RUNNING, WAITING, Scheduler
+from delta_b200.parts.base import CacheSpec, StateSpec
+from delta_b200.sampling import SamplingParams
+
+
+def manager(num_pages=16, page_size=4, max_slots=4, max_seq_len=64, window=None, states=None):
+    specs = {0: CacheSpec(2, 8), 1: CacheSpec(2, 8)}
+    if window:
+        specs[2] = CacheSpec(2, 8, window)
+    return CacheManager(specs, states or {}, max_slots=max_slots, max_seq_len=max_seq_len, page_size=page_size,
+                        num_pages=num_pages, dtype=torch.float32, device="cpu")
+
+
+def test_pool_is_lifo_and_strict():
+    p = PagePool(4)
+    a = p.alloc(3)
+    assert a == [0, 1, 2] and p.free_pages == 1
+    p.free([1])
+    assert p.alloc(1) == [1]          # the page given back last is used again first
+    with pytest.raises(OutOfPages):
+        p.alloc(2)
+    assert p.free_pages == 1          # nothing was taken by the failed call
+    p.free([0])
+    with pytest.raises(ValueError, match="twice"):
+        p.free([0])
+    with pytest.raises(ValueError):
+        p.free([7])
+    p.check()
+    assert sorted(PagePool(8, shuffle_seed=0).alloc(8)) == list(range(8))
+
+
+def test_grow_release_reuse():
+    m = manager(num_pages=6)
+    s = m.acquire_slot()
+    m.grow(s, 9)                      # 3 pages of 4 tokens
+    assert m.pages_in_use() == {"kv2x8": 3}
+    m.grow(s, 12)
+    assert m.pages_in_use() == {"kv2x8": 3}     # no page in advance at a page's edge
+    m.grow(s, 13)
+    assert m.pages_in_use() == {"kv2x8": 4}
+    t = m.acquire_slot()
+    with pytest.raises(OutOfPages):
+        m.grow(t, 12)
+    assert m.pages_in_use() == {"kv2x8": 4}     # all or nothing
+    held = m.groups["kv2x8"].held(s)
+    m.release_slot(s)
+    m.grow(t, 16)
+    assert set(m.groups["kv2x8"].held(t)) == set(held)   # pages are used again
+    with pytest.raises(ValueError, match="twice"):
+        m.release_slot(s)
+    m.check()
+
+
+def test_layers_share_a_group_and_windows_have_their_own():
+    m = manager(window=6)
+    assert set(m.groups) == {"kv2x8", "kv2x8w6"}
+    assert m.groups["kv2x8"].cache_ids == [0, 1] and m.groups["kv2x8w6"].cache_ids == [2]
+    assert m.layer_kv(1).shape == (16, 2, 2, 4, 8)
+    s = m.acquire_slot()
+    for n in range(1, 41):
+        m.grow(s, n)
+        m.advance(s, n)
+        m.check()
+        g = m.groups["kv2x8w6"]
+        # the next query (position n) reads keys n-5 .. n; earlier pages are given back
+        first_needed = max(0, n - 6 + 1) // 4
+        assert int(g.first_page[s]) == first_needed
+        assert len(g.held(s)) == (n + 3) // 4 - first_needed
+        assert len(m.groups["kv2x8"].held(s)) == (n + 3) // 4
+    assert m.groups["kv2x8w6"].pool.held_pages <= 3
+    m.release_slot(s)
+    assert m.pages_in_use() == {"kv2x8": 0, "kv2x8w6": 0}
+
+
+def test_state_slots_are_reset_at_admission():
+    m = manager(states={"toy": StateSpec((3,), torch.float32, 0.5), "count": StateSpec((), torch.int32, -1)})
+    s = m.acquire_slot()
+    assert m.states["toy"].shape == (4, 3) and m.states["count"].shape == (4,)
+    m.states["toy"][s] = 9.0
+    m.states["count"][s] = 4
+    m.release_slot(s)
+    s2 = m.acquire_slot()
+    assert s2 == s and m.states["toy"][s].tolist() == [0.5] * 3 and int(m.states["count"][s]) == -1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_lose_no_page(seed):
+    rng = random.Random(seed)
+    m = manager(num_pages=24, page_size=4, max_slots=4, max_seq_len=40, window=10)
+    live = {}
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.25 and m.free_slots:
+            live[m.acquire_slot()] = 0
+        elif op < 0.8 and live:
+            s = rng.choice(list(live))
+            n = min(40, live[s] + rng.randrange(1, 9))
+            try:
+                m.grow(s, n)
+                m.advance(s, n)
+                live[s] = n
+            except OutOfPages:
+                pass
+        elif live:
+            s = rng.choice(list(live))
+            m.release_slot(s)
+            del live[s]
+        m.check()
+        for g in m.groups.values():
+            assert g.pool.held_pages == sum(len(g.held(s)) for s in live)
+    for s in list(live):
+        m.release_slot(s)
+    assert all(v == 0 for v in m.pages_in_use().values())
+
+
+# ---- scheduler ----------------------------------------------------------------------
+
+def drive(sch, next_token=lambda r: 7, max_steps=10_000):
+    """Runs the scheduler without a model: every sampled token comes from ``next_token``."""
+    log = []
+    for _ in range(max_steps):
+        if not sch.has_work():
+            break
+        plan = sch.schedule()
+        if not plan:
+            break
+        assert sum(x.count for x in plan) <= sch.budget
+        assert len({id(x.request) for x in plan}) == len(plan)
+        log.append([(x.request.id, x.start, x.count, x.samples, x.decode) for x in plan])
+        sch.complete(plan, [next_token(x.request) for x in plan if x.samples])
+        sch.cache.check()
+    return log
+
+
+def test_budget_cuts_prompts_and_decode_goes_first():
+    m = manager(num_pages=64, page_size=4, max_slots=4, max_seq_len=64)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=10)
+    a = sch.add_request(list(range(23)), 30)
+    b = sch.add_request(list(range(5)), 12)
+    log = drive(sch)
+    assert log[0] == [(0, 0, 10, False, False)]
+    assert log[1] == [(0, 10, 10, False, False)]
+    assert log[2] == [(0, 20, 3, True, False), (1, 0, 5, True, False)]      # rest of a, then b is admitted
+    assert log[3] == [(0, 23, 1, True, True), (1, 5, 1, True, True)]
+    assert a.status == FINISHED and len(a.output) == 7 and a.finish_reason == "length"
+    assert b.status == FINISHED and len(b.output) == 7
+    assert sch.stats["prompt_tokens"] == 28 and sch.stats["generated_tokens"] == 14
+    assert all(v == 0 for v in m.pages_in_use().values()) and m.free_slots == 4
+
+
+def test_stop_token_and_max_new_tokens():
+    m = manager(num_pages=64)
+    sch = Scheduler(m, max_batch=2, max_tokens_per_step=64)
+    a = sch.add_request([1, 2, 3], 40, stop_ids=[9], max_new_tokens=None)
+    b = sch.add_request([1, 2, 3], 40, max_new_tokens=3)
+    drive(sch, next_token=lambda r: 9 if (r is a and len(r.output) == 4) else 5)
+    assert a.output == [5, 5, 5, 5, 9] and a.finish_reason == "stop token"
+    assert b.output == [5, 5, 5] and b.finish_reason == "max_new_tokens"
+
+
+def test_admission_waits_for_pages_then_reuses_them():
+    m = manager(num_pages=8, page_size=4, max_slots=4, max_seq_len=32)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=64)
+    reqs = [sch.add_request(list(range(10)), 16) for _ in range(3)]   # 3 pages for the prompt + 1 token, 4 at the end
+    log = drive(sch)
+    first = [r for r, *_ in log[0]]
+    assert first == [0, 1]            # the third request needs 3 free pages and only 2 are left
+    assert all(r.status == FINISHED and len(r.output) == 6 for r in reqs)
+    assert reqs[2].start_time >= reqs[0].start_time
+    assert sch.stats["preemptions"] == 0
+
+
+def test_out_of_pages_preempts_the_youngest_and_recomputes():
+    m = manager(num_pages=7, page_size=4, max_slots=4, max_seq_len=28)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=64)
+    a = sch.add_request(list(range(11)), 24)    # 3 pages now, 6 at the end
+    b = sch.add_request(list(range(11)), 24)
+    log = drive(sch)
+    assert a.status == FINISHED and b.status == FINISHED
+    assert len(a.output) == 13 and len(b.output) == 13
+    assert b.preemptions >= 1 and a.preemptions == 0          # the older request is never the victim
+    # after the preemption b's prompt and what it had generated run again as one portion
+    again = [row for step in log for row in step if row[0] == 1 and row[1] == 0]
+    assert len(again) == 2 and again[1][2] > 11
+    assert all(v == 0 for v in m.pages_in_use().values())
+
+
+def test_a_request_that_can_never_fit_fails_at_once():
+    m = manager(num_pages=4, page_size=4, max_slots=2, max_seq_len=64)
+    sch = Scheduler(m, max_batch=2, max_tokens_per_step=64)
+    big = sch.add_request(list(range(30)), 40)
+    too_long = sch.add_request(list(range(70)), 80)
+    ok = sch.add_request(list(range(6)), 12)
+    assert big.status == FAILED and "pages" in big.finish_reason
+    assert too_long.status == FAILED and "limit" in too_long.finish_reason
+    drive(sch)
+    assert ok.status == FINISHED and len(ok.output) == 6
+    res = sch.results()
+    assert [r["status"] for r in res] == [FAILED, FAILED, FINISHED]
+    assert set(res[2]) >= {"request_id", "status", "input_length", "output_length", "tokens_generated", "total_time", "tokens_per_second"}
+
+
+def test_prompts_first_option_holds_decoding():
+    m = manager(num_pages=64, page_size=4, max_slots=4, max_seq_len=64)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=8)
+    sch.decode_while_prefill = False
+    sch.add_request(list(range(6)), 12)
+    sch.add_request(list(range(20)), 26)
+    log = drive(sch)
+    decode_steps = [i for i, step in enumerate(log) if any(row[4] for row in step)]
+    prefill_steps = [i for i, step in enumerate(log) if any(not row[4] for row in step)]
+    assert min(decode_steps) > max(prefill_steps)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_load_finishes_everything(seed):
+    rng = random.Random(seed)
+    m = manager(num_pages=20, page_size=4, max_slots=3, max_seq_len=48, window=9)
+    sch = Scheduler(m, max_batch=3, max_tokens_per_step=rng.choice([5, 16, 64]))
+    reqs = [sch.add_request([1] * rng.randrange(1, 30), rng.randrange(8, 48)) for _ in range(12)]
+    drive(sch, next_token=lambda r: rng.randrange(10))
+    for r in reqs:
+        assert r.status in (FINISHED, FAILED)
+        if r.status == FINISHED:
+            assert r.total_len >= min(r.max_length, 48) or r.finish_reason != "length"
+    assert all(v == 0 for v in m.pages_in_use().values()) and m.free_slots == 3

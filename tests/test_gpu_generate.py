@@ -1,0 +1,123 @@
+"""Generation through the Python entry point and the command line; long decoding; the
+first tokens of a sequence; temperature sampling."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import helpers
+from plain_yi import PlainYi, greedy, temperature_probs
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def plain_greedy(plain, prompt, n):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = greedy(plain.forward(seq)[-1])
+        out.append(t)
+        seq.append(t)
+    return out
+
+
+def backend(folder, dtype, **kw):
+    from delta_b200.engine import LMBackend
+    e = LMBackend(dtype=dtype, device="cuda:0")
+    e.load_model(folder)
+    e.setup_caches(check_kernel_errors=True, **kw)
+    return e
+
+
+def test_greedy_generation_matches_plain(model_folders):
+    folder = model_folders["A"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(n, plain.cfg.vocab, 5 + i) for i, n in enumerate([5, 17, 33])]
+    e = backend(folder, "float32", max_batch_size=4, max_seq_length=64, page_size=16)
+    outs = e.generate(prompts, 8)
+    for p, o in zip(prompts, outs):
+        assert o == plain_greedy(plain, p, 8)
+    res = e.get_detailed_results()
+    assert [r["output_length"] for r in res] == [8, 8, 8] and all(r["status"] == "finished" for r in res)
+
+
+def test_generation_with_few_pages_and_a_small_budget(model_folders):
+    """More requests than slots, prompts cut into portions of at most 11 tokens, a pool that
+    forces waiting; the tokens still equal the plain implementation's."""
+    folder = model_folders["C"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(n, plain.cfg.vocab, 50 + i) for i, n in enumerate([3, 50, 75, 20, 41, 9])]
+    e = backend(folder, "float32", max_batch_size=3, max_seq_length=96, page_size=32, num_pages=7, max_tokens_per_step=11)
+    outs = e.generate(prompts, 6)
+    for p, o in zip(prompts, outs):
+        assert o == plain_greedy(plain, p, 6)
+    assert e.scheduler.stats["prefill_steps"] > 6
+    e.runner.cache.check()
+    assert all(v == 0 for v in e.runner.cache.pages_in_use().values())
+
+
+def test_long_decoding(model_folders):
+    """200 tokens decoded one by one from a short prompt, against the plain implementation
+    run on the whole sequence (float32 logits, and greedy tokens)."""
+    from delta_b200.engine.step import RowInput
+    folder = model_folders["B"]
+    plain = PlainYi(folder)
+    e = backend(folder, "float32", max_batch_size=1, max_seq_length=256, page_size=8)
+    prompt = helpers.random_tokens(4, plain.cfg.vocab, 9)
+    out = e.generate([prompt], 200)[0]
+    seq = prompt + out
+    ref = plain.forward(seq[:-1])
+    for i, t in enumerate(out):
+        assert t == greedy(ref[len(prompt) - 1 + i]), f"token {i}"
+
+
+def test_first_tokens(model_folders):
+    """Positions 0, 1, 2 of a sequence, fed one by one and as one portion."""
+    from delta_b200.config import EngineConfig
+    from delta_b200.engine.step import ModelRunner
+    for which in "AB":
+        folder = model_folders[which]
+        plain = PlainYi(folder)
+        toks = [helpers.random_tokens(3, plain.cfg.vocab, 3), helpers.random_tokens(1, plain.cfg.vocab, 4)]
+        refs = [plain.forward(t) for t in toks]
+        r = ModelRunner(folder, engine_config=EngineConfig(max_batch=2, max_seq_len=32, page_size=helpers.PAGE_SIZE[which], dtype="float32"))
+        for steps in ([[(0, 0, 3)], [(1, 0, 1)]], [[(0, 0, 1), (1, 0, 1)], [(0, 1, 1)], [(0, 2, 1)]]):
+            res = helpers.run_schedule(r, toks, steps)
+            for i, t in enumerate(toks):
+                assert torch.allclose(helpers.stack_positions(res, i, len(t)), refs[i], atol=2e-5, rtol=1e-4)
+
+
+def test_temperature_sampling_follows_the_distribution(model_folders):
+    """Each sampled token is the one whose interval of the cumulative distribution
+    (vocabulary order) holds the request's uniform number for that position."""
+    from delta_b200.sampling import uniform_of
+    folder = model_folders["B"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(n, plain.cfg.vocab, 20 + i) for i, n in enumerate([1, 9, 40])]
+    e = backend(folder, "float32", max_batch_size=4, max_seq_length=128, page_size=8)
+    outs = e.generate(prompts, 12, temperature=0.7, seed=1234)
+    again = backend(folder, "float32", max_batch_size=2, max_seq_length=128, page_size=8, max_tokens_per_step=7)
+    assert again.generate(prompts, 12, temperature=0.7, seed=1234) == outs   # same seed, other batching: same tokens
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        seq = list(p)
+        for t in o:
+            probs = temperature_probs(plain.forward(seq)[-1], 0.7)
+            cdf = torch.cumsum(probs, 0)
+            u = uniform_of(1234 + i, len(seq))
+            lo = cdf[t - 1].item() if t > 0 else 0.0
+            assert lo - 1e-5 <= u <= cdf[t].item() + 1e-5, (i, len(seq), t, u, lo, cdf[t].item())
+            seq.append(t)
+
+
+def test_command_line(model_folders, tmp_path):
+    out = tmp_path / "result.json"
+    cmd = [sys.executable, "-m", "delta_b200.cli", "--model", str(model_folders["A"]), "--B", "4", "--max_len", "128",
+           "--dataset", "random", "--prompt_len", "20", "--num_samples", "5", "--max_new_tokens", "6", "--dtype", "float32",
+           "--enable_selective_cache", "--full_cache_layers", "0", "--subset_cache_size", "2", "--L", "1", "--out", str(out)]
+    r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = json.loads(out.read_text())
+    assert res["summary"]["generated_tokens"] == 30 and len(res["results"]) == 5

@@ -1,0 +1,86 @@
+"""DELTA's selective cache on the GPU against the plain implementation that attends
+to the same chosen pages: logits, page scores and the chosen pages themselves."""
+import pytest
+import torch
+
+import helpers
+from plain_yi import PlainYi, Selective
+from test_gpu_model import TOL, compare
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # which, full_cache_layers, k, L, ratio
+    ("B", (1,), 4, 8, 1.0),      # layer 0 reads the last 4 pages, layer 1 plans, layer 2 reads the chosen pages
+    ("B", (0,), 3, 1, 1.0),
+    ("A", (0,), 2, 1, 1.5),      # selection starts only when pages / k > 1.5
+    ("C", (0,), 2, 1, 1.0),      # layer 0 plans for layer 2; the windowed layers 1 and 3 take no selection
+    ("B", (0, 1), 2, 2, 1.0),    # two full layers, the second one plans
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which, full, k, L, ratio", CASES)
+def test_selective_cache(model_folders, which, full, k, L, ratio, dtype):
+    from delta_b200.config import EngineConfig, SelectiveCacheConfig
+    from delta_b200.engine.step import ModelRunner
+    folder = model_folders[which]
+    ps = helpers.PAGE_SIZE[which]
+    sel = SelectiveCacheConfig(full_cache_layers=full, subset_cache_size=k, L=L, compression_ratio=ratio)
+    lengths = [30, 70, 110, 150]
+    prompt_lens = [9, 20, 35, 40]
+    plain = PlainYi(folder, rounding="bfloat16" if dtype == "bfloat16" else None)
+    toks = [helpers.random_tokens(n, plain.cfg.vocab, 40 + i) for i, n in enumerate(lengths)]
+    refs, chosen = [], []
+    for t, pl in zip(toks, prompt_lens):
+        refs.append(plain.forward(t, Selective(list(full), k, L, ratio, ps, pl)))
+        chosen.append(dict(plain.last_selection))
+    assert any(chosen), "the case never selected anything"
+
+    def runner(num_pages):
+        cfg = EngineConfig(max_batch=4, max_seq_len=256, page_size=ps, num_pages=num_pages, dtype=dtype, selective=sel)
+        return ModelRunner(folder, engine_config=cfg)
+
+    # each request alone: the prompt in one step, then token by token
+    steps = []
+    for i, (n, pl) in enumerate(zip(lengths, prompt_lens)):
+        steps.append([(i, 0, pl)])
+        steps.extend([[(i, p, 1)] for p in range(pl, n)])
+    r = runner(4 * (256 // ps))
+    res = helpers.run_schedule(r, toks, steps, prompt_lens=prompt_lens, selective=True)
+    compare(res, refs, lengths, dtype, "alone")
+
+    # prompts in portions, decode tokens of several requests in one step, few pages
+    sched, ends = helpers.mixed(lengths, prompt_lens, seed=5)
+    r2 = runner(helpers.peak_pages(sched, ends, ps))
+    res = helpers.run_schedule(r2, toks, sched, ends, prompt_lens=prompt_lens, selective=True)
+    compare(res, refs, lengths, dtype, "mixed")
+
+
+def test_chosen_pages_equal_the_plain_ones(model_folders):
+    """One request, float32: after every decode step the state slot holds exactly the
+    pages that the plain implementation chose for that position."""
+    from delta_b200.config import EngineConfig, SelectiveCacheConfig
+    from delta_b200.engine.step import ModelRunner, RowInput
+    from delta_b200.parts.attention import SELECTED_COUNT, SELECTED_PAGES
+    folder, ps, k = model_folders["B"], helpers.PAGE_SIZE["B"], 4
+    sel = SelectiveCacheConfig(full_cache_layers=(1,), subset_cache_size=k, L=2)
+    plain = PlainYi(folder)
+    n, pl = 120, 16
+    toks = helpers.random_tokens(n, plain.cfg.vocab, 77)
+    plain.forward(toks, Selective([1], k, 2, 1.0, ps, pl))
+    want = plain.last_selection
+    r = ModelRunner(folder, engine_config=EngineConfig(max_batch=2, max_seq_len=128, page_size=ps, dtype="float32", selective=sel))
+    slot = r.cache.acquire_slot()
+    r.run_rows([RowInput(slot, toks[:pl], 0, [])])
+    checked = 0
+    for p in range(pl, n):
+        r.run_rows([RowInput(slot, toks[p:p + 1], p, [0], selective=True)])
+        count = int(r.cache.states[SELECTED_COUNT][slot])
+        if (2, p) in want:
+            assert count == k
+            assert r.cache.states[SELECTED_PAGES][slot, :count].tolist() == want[(2, p)], f"position {p}"
+            checked += 1
+        else:
+            assert count == -1
+    assert checked > 50
