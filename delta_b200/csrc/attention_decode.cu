@@ -1,0 +1,403 @@
+// Paged decode attention for bfloat16: one new token per request, the keys split
+// over several thread blocks, the query heads of one key-value head packed as the
+// rows of a tensor-core tile.
+//
+// Grid (splits, kv heads, batch rows); 4 warps per block.  A block walks its share of
+// the request's pages in tiles of 64 keys.  K and V tiles come into shared memory
+// with cp.async (3 stages), 16-byte chunks swizzled so that ldmatrix reads without
+// bank conflicts.  Each warp owns 16 keys of a tile: S = Q K^T with
+// mma.sync.m16n8k16 (rows = the G <= 16 query heads of the group), an online softmax
+// in float on its own keys, then O += P V.  The four warps are merged through shared
+// memory at the end; with more than one split the block writes (m, l, O) to the
+// scratch buffer and a second kernel merges the splits in a fixed order.
+//
+// The kernel is bound by the bytes of K and V it has to read once; the tensor-core
+// work is small beside it, which is why the legacy warp-level MMA is enough here.
+//
+// It takes: the whole cache, a window of it, or the list of chosen pages of DELTA's
+// subset layers; and it can dump the scaled scores and the log-sum-exp for DELTA's
+// page scoring (reference: backend.py:191-221, 562-577).
+#include "common.cuh"
+#include "attention_params.h"
+
+namespace {
+constexpr int TILE = 64;     // keys per tile
+constexpr int STAGES = 3;
+constexpr int NWARPS = 4;
+constexpr int NTHREADS = NWARPS * 32;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // size 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct RowInfo {
+  int t, pos, lo, slot, n_entries, first_page;
+  bool subset, dumping;
+  const int* sel;
+};
+
+__device__ __forceinline__ RowInfo row_info(const DkAttnParams& p, int row) {
+  RowInfo r;
+  r.t = p.row_q_start[row] + p.row_q_len[row] - 1;
+  r.pos = p.tok_pos[r.t];
+  r.slot = p.row_slot ? p.row_slot[row] : row;
+  const int flags = p.row_flags ? p.row_flags[row] : 0;
+  int n_sel = -1;
+  if (p.sel_pages != nullptr && (flags & 1)) n_sel = p.sel_count[r.slot];
+  r.subset = n_sel >= 0;
+  r.lo = (p.window > 0 && r.pos - p.window + 1 > 0) ? r.pos - p.window + 1 : 0;
+  r.first_page = r.lo / p.ps;
+  r.n_entries = r.subset ? n_sel : (r.pos / p.ps - r.first_page + 1);
+  r.sel = r.subset ? p.sel_pages + (size_t)r.slot * p.sel_stride : nullptr;
+  r.dumping = p.dump != nullptr && (flags & 1);
+  return r;
+}
+
+// scratch layout per (row, head, split): HD floats of O, then m and l at the end of the buffer
+__device__ __forceinline__ size_t part_o_index(const DkAttnParams& p, int row, int h, int split, int HD) {
+  return (((size_t)row * p.H + h) * p.splits + split) * HD;
+}
+__device__ __forceinline__ size_t part_ml_index(const DkAttnParams& p, int row, int h, int split) {
+  return (size_t)p.rows * p.H * p.splits * p.hd + (((size_t)row * p.H + h) * p.splits + split) * 2;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkAttnParams p) {
+  constexpr int CHUNKS = HD / 8;              // 16-byte chunks per key row
+  constexpr int ROW_BYTES = HD * 2;
+  constexpr int TILE_BYTES = TILE * ROW_BYTES;  // one of K or V
+  constexpr int KB = HD / 16;                 // k-blocks of the QK product
+  constexpr int NT = HD / 8;                  // n-tiles of the PV product
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* kv_smem = smem;                                  // STAGES * 2 * TILE_BYTES
+  int* s_key = reinterpret_cast<int*>(smem + STAGES * 2 * TILE_BYTES);  // STAGES * TILE key positions (-1: no key)
+
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int G = p.H / p.KV, ps = p.ps;
+  const RowInfo ri = row_info(p, row);
+  const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(p.kv);
+
+  // this block's share of the pages
+  const int per = (ri.n_entries + p.splits - 1) / p.splits;
+  const int e_begin = split * per;
+  const int e_end = min(ri.n_entries, e_begin + per);
+  const int pages_per_tile = TILE / ps;
+  const int n_tiles = e_end > e_begin ? (e_end - e_begin + pages_per_tile - 1) / pages_per_tile : 0;
+
+  // the query heads of this group as A fragments: rows g and g + 8
+  uint32_t qa[KB][4];
+  {
+    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)ri.t * p.q_stride + (size_t)kvh * G * HD;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+      const int c = kb * 16 + 2 * tq;
+      qa[kb][0] = g < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + c) : 0u;
+      qa[kb][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c) : 0u;
+      qa[kb][2] = g < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + c + 8) : 0u;
+      qa[kb][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c + 8) : 0u;
+    }
+  }
+
+  auto load_tile = [&](int tile, int stage) {
+    unsigned char* kdst = kv_smem + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* vdst = kdst + TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < TILE * CHUNKS / NTHREADS; ++i) {
+      const int c = tid + i * NTHREADS;
+      const int tok = c / CHUNKS, part = c % CHUNKS;
+      const int e = e_begin + tile * pages_per_tile + tok / ps, off = tok % ps;
+      bool valid = false;
+      size_t koff = 0;
+      int key = -1;
+      if (e < e_end) {
+        const int lp = ri.subset ? ri.sel[e] : ri.first_page + e;
+        const int k = lp * ps + off;
+        if (lp >= 0 && lp < p.max_pages && k >= ri.lo && k <= ri.pos) {
+          const int page = p.block_table[(size_t)row * p.max_pages + lp];
+          if (page >= 0 && page < p.num_pages) {
+            valid = true;
+            key = k;
+            koff = ((((size_t)page * 2 + 0) * p.KV + kvh) * ps + off) * HD + part * 8;
+          } else if (part == 0) {
+            dk_report(p.err, DK_DEV_BAD_PAGE, ri.t, lp, page);
+          }
+        }
+      }
+      const int sw = (part ^ (tok & 7)) * 16;
+      cp_async_16(smem_u32(kdst + tok * ROW_BYTES + sw), kv + koff, valid);
+      cp_async_16(smem_u32(vdst + tok * ROW_BYTES + sw), kv + koff + (size_t)p.KV * ps * HD, valid);
+      if (part == 0) s_key[stage * TILE + tok] = key;
+    }
+  };
+
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // rows g and g + 8, in units of log2
+  float l_run[2] = {0.f, 0.f};              // this thread's part of the row sums
+  const float sc_log2 = p.scale * 1.4426950408889634f;
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_tiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = tile + STAGES - 1;
+      if (nxt < n_tiles) load_tile(nxt, nxt % STAGES);
+      cp_async_commit();
+    }
+    const int stage = tile % STAGES;
+    const uint32_t kbase = smem_u32(kv_smem + (size_t)stage * 2 * TILE_BYTES);
+    const uint32_t vbase = kbase + TILE_BYTES;
+    const int* keys = s_key + stage * TILE + warp * 16;
+
+    // S = Q K^T for this warp's 16 keys (two n-tiles of 8)
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int tok = warp * 16 + j * 8 + (lane & 7);
+#pragma unroll
+      for (int kb = 0; kb < KB; kb += 2) {
+        const int chunk = 2 * kb + (lane >> 3);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, kbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
+        mma_bf16(s[j], qa[kb], b0, b1);
+        mma_bf16(s[j], qa[kb + 1], b2, b3);
+      }
+    }
+    // mask, dump, online softmax (values in log2 units)
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int key = keys[j * 8 + 2 * tq + c];
+        if (key < 0) {
+          s[j][c] = -INFINITY;
+          s[j][2 + c] = -INFINITY;
+        } else {
+          if (ri.dumping && key < p.dump_stride) {
+            if (g < G) p.dump[((size_t)row * p.H + kvh * G + g) * p.dump_stride + key] = s[j][c] * p.scale;
+            if (g + 8 < G) p.dump[((size_t)row * p.H + kvh * G + g + 8) * p.dump_stride + key] = s[j][2 + c] * p.scale;
+          }
+          s[j][c] *= sc_log2;
+          s[j][2 + c] *= sc_log2;
+        }
+        tmax[0] = fmaxf(tmax[0], s[j][c]);
+        tmax[1] = fmaxf(tmax[1], s[j][2 + c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float m_new = fmaxf(m_run[r], tmax[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;   // a warp whose 16 keys are all masked
+      corr[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+    uint32_t pa[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        pv[j][0] = exp2f(s[j][0] - m_use[0]);
+        pv[j][1] = exp2f(s[j][1] - m_use[0]);
+        pv[j][2] = exp2f(s[j][2] - m_use[1]);
+        pv[j][3] = exp2f(s[j][3] - m_use[1]);
+        l_run[0] += pv[j][0] + pv[j][1];
+        l_run[1] += pv[j][2] + pv[j][3];
+      }
+      pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+      pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+      pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+      pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+    }
+    // O = O * corr + P V
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
+    {
+      const int tok = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        const int chunk = n + (lane >> 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
+        mma_bf16(o[n], pa, b0, b1);
+        mma_bf16(o[n + 1], pa, b2, b3);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps through shared memory (the tiles are no longer needed)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float* w_o = reinterpret_cast<float*>(smem);         // [NWARPS][16][HD]
+  float* w_m = w_o + NWARPS * 16 * HD;                 // [NWARPS][16]
+  float* w_l = w_m + NWARPS * 16;                      // [NWARPS][16]
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    float* base = w_o + ((size_t)warp * 16) * HD + n * 8 + 2 * tq;
+    base[(size_t)g * HD] = o[n][0];
+    base[(size_t)g * HD + 1] = o[n][1];
+    base[(size_t)(g + 8) * HD] = o[n][2];
+    base[(size_t)(g + 8) * HD + 1] = o[n][3];
+  }
+  if (tq == 0) {
+    w_m[warp * 16 + g] = m_run[0];
+    w_m[warp * 16 + g + 8] = m_run[1];
+    w_l[warp * 16 + g] = l_run[0];
+    w_l[warp * 16 + g + 8] = l_run[1];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * HD; idx += NTHREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, w_m[w * 16 + r]);
+    float L = 0.f, acc = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) {
+        const float mw = w_m[w * 16 + r];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        L += w_l[w * 16 + r] * f;
+        acc += w_o[((size_t)w * 16 + r) * HD + d] * f;
+      }
+    }
+    const int h = kvh * G + r;
+    if (p.splits == 1) {
+      reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)ri.t * p.H * HD + (size_t)h * HD + d] =
+          __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      if (p.lse != nullptr && d == 0) p.lse[(size_t)ri.t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
+    } else {
+      float* sc = reinterpret_cast<float*>(p.scratch);
+      sc[part_o_index(p, row, h, split, HD) + d] = acc;
+      if (d == 0) {
+        sc[part_ml_index(p, row, h, split)] = M;
+        sc[part_ml_index(p, row, h, split) + 1] = L;
+      }
+    }
+  }
+}
+
+// Merges the splits of one (row, head) in split order.
+template <int HD>
+__global__ void attention_decode_merge_kernel(const DkAttnParams p) {
+  const int row = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const float* sc = reinterpret_cast<const float*>(p.scratch);
+  const int t = p.row_q_start[row] + p.row_q_len[row] - 1;
+  float M = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, sc[part_ml_index(p, row, h, s)]);
+  float L = 0.f, acc = 0.f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < p.splits; ++s) {
+      const float ms = sc[part_ml_index(p, row, h, s)];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += sc[part_ml_index(p, row, h, s) + 1] * f;
+      if (d < HD) acc += sc[part_o_index(p, row, h, s, HD) + d] * f;
+    }
+  }
+  if (d < HD)
+    reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.H * HD + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
+}
+
+template <int HD>
+int launch(const DkAttnParams& p, cudaStream_t stream) {
+  constexpr size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int);
+  constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
+  constexpr size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  dim3 grid(p.splits, p.KV, p.rows);
+  attention_decode_kernel<HD><<<grid, NTHREADS, smem, stream>>>(p);
+  int rc = dk_check_launch("attention_decode");
+  if (rc != 0 || p.splits == 1) return rc;
+  dim3 mgrid(p.H, p.rows);
+  attention_decode_merge_kernel<HD><<<mgrid, HD, 0, stream>>>(p);
+  return dk_check_launch("attention_decode_merge");
+}
+}  // namespace
+
+// Floats of scratch that a launch with these sizes needs (0 when splits == 1).
+extern "C" long long dk_attention_decode_scratch_floats(int rows, int H, int hd, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)rows * H * splits * (hd + 2);
+}
+
+// 1 when the fast kernel takes these sizes, else 0 (the caller then uses the plain kernel).
+extern "C" int dk_attention_decode_supported(int dtype, int H, int KV, int hd, int ps) {
+  if (dtype != DK_BF16 || KV <= 0 || H % KV != 0) return 0;
+  if (H / KV > 16) return 0;
+  if (hd != 64 && hd != 128) return 0;
+  if (ps < 1 || ps > TILE || (ps & (ps - 1)) != 0) return 0;
+  return 1;
+}
+
+extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) {
+  const DkAttnParams& p = *pp;
+  if (p.rows == 0) return 0;
+  DK_REQUIRE(dk_attention_decode_supported(p.dtype, p.H, p.KV, p.hd, p.ps),
+             "attention_decode: sizes not taken (bfloat16, head size 64 or 128, at most 16 query heads per key-value head, "
+             "page size a power of two <= 64): dtype=%d H=%d KV=%d hd=%d ps=%d", p.dtype, p.H, p.KV, p.hd, p.ps);
+  DK_REQUIRE(p.T == p.rows, "attention_decode: %d tokens for %d rows; every row must bring one token", p.T, p.rows);
+  DK_REQUIRE(p.row_q_start != nullptr && p.row_q_len != nullptr, "attention_decode: row_q_start / row_q_len are missing");
+  DK_REQUIRE(p.splits >= 1 && p.splits <= 65535 && p.KV <= 65535 && p.rows <= 65535, "attention_decode: grid too large");
+  DK_REQUIRE(p.splits == 1 || p.scratch != nullptr, "attention_decode: %d splits need a scratch buffer", p.splits);
+  DK_REQUIRE(p.q_stride % 2 == 0, "attention_decode: q stride must be even");
+  DK_REQUIRE(p.sel_pages == nullptr || (p.sel_count != nullptr && p.row_flags != nullptr && p.row_slot != nullptr),
+             "attention_decode: chosen pages are given without their counts, row flags or slots");
+  return p.hd == 64 ? launch<64>(p, stream) : launch<128>(p, stream);
+}

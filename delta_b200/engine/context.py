@@ -48,6 +48,7 @@ class StepContext:
         self.plain_products = plain_products
         self.plain_attention = plain_attention
         self.capture = capture
+        self.fixed_decode_splits = 0   # set by the decode graph: a captured launch keeps its grid
         self._scratch_pool = scratch_pool
         self._once = set()
 

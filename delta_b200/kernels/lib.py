@@ -48,6 +48,10 @@ _SIGNATURES = {
     "dk_page_scores": [P, P, P, P, P, P, P, I, I, I, I, I, I, D, P],
     "dk_select_pages": [P, P, P, P, P, P, P, I, I, I, I, I, F, D, P],
     "dk_sample": [P, I, I, I, P, P, P, P, P, P, P],
+    "dk_attention_decode": [C.POINTER(AttnParams), P],
+    "dk_attention_decode_supported": [I, I, I, I, I],
+    "dk_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, I, P],
+    "dk_gemm_small_m_supported": [I, I, I, I],
 }
 
 
@@ -64,6 +68,8 @@ def load():
         lib.dk_last_error.restype = C.c_char_p
         lib.dk_last_error.argtypes = []
         lib.dk_sizeof_attn_params.restype = I
+        lib.dk_attention_decode_scratch_floats.restype = C.c_longlong
+        lib.dk_attention_decode_scratch_floats.argtypes = [I, I, I, I]
         if lib.dk_sizeof_attn_params() != C.sizeof(AttnParams):
             raise KernelError(f"AttnParams is {C.sizeof(AttnParams)} bytes in Python and "
                               f"{lib.dk_sizeof_attn_params()} in the library: the two declarations differ")

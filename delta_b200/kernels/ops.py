@@ -178,6 +178,39 @@ def attention_plain(params: AttnParams):
     _l.check(_l.load().dk_attention_plain(C.byref(params), _stream()), "attention_plain")
 
 
+def attention_decode_supported(dtype, H, KV, hd, ps) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_l.load().dk_attention_decode_supported(BF16, H, KV, hd, ps))
+
+
+def attention_decode_scratch_floats(rows, H, hd, splits) -> int:
+    return int(_l.load().dk_attention_decode_scratch_floats(rows, H, hd, splits))
+
+
+def attention_decode(params: AttnParams):
+    """One new token per row; ``params.splits`` blocks share a request's keys and, when there
+    is more than one, ``params.scratch`` holds their partial results."""
+    _l.check(_l.load().dk_attention_decode(C.byref(params), _stream()), "attention_decode", 2 if params.splits > 1 else 1)
+
+
+def gemm_small_m_supported(M, N, K, swiglu=False) -> bool:
+    return bool(_l.load().dk_gemm_small_m_supported(M, N, K, int(swiglu)))
+
+
+def gemm_small_m(x, w, out, swiglu=False):
+    """out = x @ w^T for up to 64 rows of bfloat16 x, streaming w once.  ``swiglu``: w holds
+    gate rows then up rows, and out [M, N/2] = silu(x gate^T) * (x up^T)."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_small_m: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} or dtypes do not fit")
+    _l.check(_l.load().dk_gemm_small_m(_ptr(x, "x"), _ptr(w, "w"), _ptr(out, "out"), M, N, K, x.stride(0), w.stride(0),
+                                       out.stride(0), dtype_code(out.dtype), int(swiglu), _stream()), "gemm_small_m")
+    return out
+
+
 def recent_pages(row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, ps, ratio):
     i32 = torch.int32
     _l.check(_l.load().dk_recent_pages(_ptr(row_slot, "row_slot", i32), _ptr(row_flags, "row_flags", i32),

@@ -32,7 +32,9 @@ class SwiGLU(FeedForward):
         self.w_down = tensors[p + "down_proj.weight"]
 
     def forward(self, ctx, x):
-        gu = linear.linear(ctx, x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, act)
+        act = linear.swiglu_linear(ctx, x, self.w_gate_up)
+        if act is None:
+            gu = linear.linear(ctx, x, self.w_gate_up)
+            act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+            ops.silu_mul(gu, act)
         return linear.linear(ctx, act, self.w_down)

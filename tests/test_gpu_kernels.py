@@ -1,0 +1,448 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same op, at
+sizes other than the engine's tiny models use (head sizes in steps of 16, odd numbers of
+heads and groups, widths and vocabularies that are no power of two)."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from delta_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------ elementwise
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    o = ops()
+    table = torch.randn(777, 72, device=DEV).to(dtype)
+    tok = i32([0, 776, 5, 5, 300])
+    out = torch.empty(5, 72, dtype=dtype, device=DEV)
+    o.embedding(tok, table, out)
+    assert torch.equal(out, table[tok.long()])
+    err = o.new_error_record(DEV)
+    o.embedding(i32([3, 777]), table, out[:2], err=err)
+    with pytest.raises(Exception, match="token id out of range"):
+        o.raise_if_error(err)
+
+
+@pytest.mark.parametrize("dtype, wdtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("d", [48, 1000, 4096])
+def test_rms_norm(dtype, wdtype, d):
+    o = ops()
+    x = torch.randn(7, d, device=DEV).to(dtype)
+    add = torch.randn(7, d, device=DEV).to(dtype)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(wdtype)
+    eps = 3e-6
+
+    def ref(v, cast_first):
+        v = v.float()
+        n = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+        if cast_first:
+            n = n.to(dtype).float()
+        return (n * w.float()).to(dtype)
+
+    for cast_first in (False, True):
+        out = torch.empty_like(x)
+        o.rms_norm(x.clone(), w, eps, out, cast_first=cast_first)
+        assert torch.allclose(out.float(), ref(x, cast_first).float(), **tol(dtype))
+    # fused residual add on chosen rows: x[rows] += add[rows] in place, the other rows stay
+    rows = i32([5, 0, 2])
+    xs = x.clone()
+    out = torch.empty(3, d, dtype=dtype, device=DEV)
+    o.rms_norm(xs, w, eps, out, add=add, rows=rows)
+    summed = (x.float() + add.float()).to(dtype)
+    assert torch.equal(xs[[5, 0, 2]], summed[[5, 0, 2]]) and torch.equal(xs[[1, 3, 4, 6]], x[[1, 3, 4, 6]])
+    assert torch.allclose(out.float(), ref(summed[[5, 0, 2]], False).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    o = ops()
+    gu = (torch.randn(9, 2 * 344, device=DEV) * 3).to(dtype)
+    out = torch.empty(9, 344, dtype=dtype, device=DEV)
+    o.silu_mul(gu, out)
+    g, u = gu[:, :344].float(), gu[:, 344:].float()
+    assert torch.allclose(out.float(), (torch.nn.functional.silu(g) * u).to(dtype).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_append(dtype, interleaved):
+    from delta_b200.parts.rope import RotaryPositions
+    o = ops()
+    H, KV, hd, ps, pages = 6, 3, 48, 8, 10
+    T = 11
+    rope = RotaryPositions(hd, 250000.0, 64, interleaved)
+    table = rope.table(torch.device(DEV))
+    qkv = torch.randn(T, (H + 2 * KV) * hd, device=DEV).to(dtype)
+    pos = [0, 1, 2, 3, 4, 5, 6, 7, 8, 30, 31]      # request 0 crosses a page's edge; request 1 sits at its end
+    row = [0] * 9 + [1, 1]
+    bt = i32([[7, 2, -1, -1], [4, 9, 1, 5]])
+    kv = torch.zeros(pages, 2, KV, ps, hd, dtype=dtype, device=DEV)
+    orig = qkv.clone()
+    o.rope_append(qkv, i32(pos), i32(row), bt, kv, table, H, KV, hd, ps, interleaved)
+    half = hd // 2
+    v3 = orig.float().view(T, H + 2 * KV, hd)
+    for t in range(T):
+        c, s = table[pos[t], :, 0], table[pos[t], :, 1]
+        x = v3[t, :H + KV]
+        if interleaved:
+            a, b = x[:, 0::2], x[:, 1::2]
+            r = torch.empty_like(x)
+            r[:, 0::2], r[:, 1::2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[:, :half], x[:, half:]
+            r = torch.cat([a * c - b * s, a * s + b * c], -1)
+        r = r.to(dtype)
+        got = qkv[t].view(H + 2 * KV, hd)
+        assert torch.allclose(got[:H].float(), r[:H].float(), **tol(dtype))
+        page = int(bt[row[t], pos[t] // ps])
+        assert torch.allclose(kv[page, 0, :, pos[t] % ps].float(), r[H:].float(), **tol(dtype))
+        assert torch.equal(kv[page, 1, :, pos[t] % ps], orig[t].view(H + 2 * KV, hd)[H + KV:])
+    assert kv[[0, 3, 6, 8]].abs().sum() == 0            # pages of nobody stay untouched
+    # without a table nothing is rotated; without a cache nothing is appended
+    q2 = orig.clone()
+    o.rope_append(q2, i32(pos), i32(row), bt, None, None, H, KV, hd, ps, interleaved)
+    assert torch.equal(q2, orig)
+    # a position without a page is reported, not written
+    err = o.new_error_record(DEV)
+    o.rope_append(orig.clone()[:1], i32([20]), i32([0]), bt, kv, table, H, KV, hd, ps, interleaved, err=err)
+    with pytest.raises(Exception, match="page id out of range"):
+        o.raise_if_error(err)
+
+
+# ------------------------------------------------------------------ matrix products
+
+@pytest.mark.parametrize("M, N, K", [(1, 48, 40), (5, 1000, 344), (70, 130, 257), (129, 64, 16)])
+def test_gemm_plain_float32_is_true_32_bit(M, N, K):
+    o = ops()
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    o.gemm_nt_plain(a, w, out)
+    ref = (a.double() @ w.double().T)
+    assert torch.allclose(out.double(), ref, atol=1e-4, rtol=1e-5)   # a tf32 product would miss this by 1e-2
+    # the sum over k does not depend on how many rows share the batch
+    one = torch.empty(1, N, device=DEV)
+    o.gemm_nt_plain(a[M // 2:M // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 17, 33, 64])
+@pytest.mark.parametrize("N, K", [(96, 40), (1056, 344), (4096, 4096)])
+def test_gemm_small_m(M, N, K):
+    o = ops()
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    o.gemm_small_m(x, w, out)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2)
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    o.gemm_small_m(x, w, out32)
+    assert torch.allclose(out32, ref, atol=1e-3, rtol=1e-4)
+    # SwiGLU epilogue: rows [0, N/2) are the gate, rows [N/2, N) the up projection
+    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+    o.gemm_small_m(x, w, act, swiglu=True)
+    want = torch.nn.functional.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+    assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_gemm_small_m_refuses_what_it_does_not_take():
+    o = ops()
+    assert not o.gemm_small_m_supported(65, 64, 64)
+    assert not o.gemm_small_m_supported(4, 50, 64)      # columns no multiple of 16
+    assert not o.gemm_small_m_supported(4, 64, 36)      # K no multiple of 8
+    x = torch.zeros(4, 36, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 36, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="sizes not taken"):
+        o.gemm_small_m(x, w, torch.empty(4, 64, dtype=torch.bfloat16, device=DEV))
+
+
+# ------------------------------------------------------------------ attention
+
+class PagedCase:
+    """Random requests in a random paged cache, with the plain float32 answer."""
+
+    def __init__(self, dtype, H, KV, hd, ps, seq_lens, q_lens, seed=0, scatter=True):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.dtype, self.H, self.KV, self.hd, self.ps = dtype, H, KV, hd, ps
+        self.seq_lens, self.q_lens = seq_lens, q_lens
+        B = len(seq_lens)
+        max_pages = max((n + ps - 1) // ps for n in seq_lens) + 1
+        total = sum((n + ps - 1) // ps for n in seq_lens)
+        ids = list(range(total + 3))
+        if scatter:
+            random.Random(seed).shuffle(ids)
+        self.k = [torch.randn(n, KV, hd, generator=g).to(dtype) for n in seq_lens]
+        self.v = [torch.randn(n, KV, hd, generator=g).to(dtype) for n in seq_lens]
+        self.q = [torch.randn(ql, H, hd, generator=g).to(dtype) for ql in q_lens]
+        kv = torch.zeros(total + 3, 2, KV, ps, hd, dtype=dtype)
+        bt = torch.full((B, max_pages), -1, dtype=torch.int32)
+        nxt = 0
+        for b, n in enumerate(seq_lens):
+            for lp in range((n + ps - 1) // ps):
+                page = ids[nxt]
+                nxt += 1
+                bt[b, lp] = page
+                cnt = min(ps, n - lp * ps)
+                kv[page, 0, :, :cnt] = self.k[b][lp * ps:lp * ps + cnt].transpose(0, 1)
+                kv[page, 1, :, :cnt] = self.v[b][lp * ps:lp * ps + cnt].transpose(0, 1)
+        self.kv, self.bt = kv.to(DEV), bt.to(DEV)
+        tok_row, tok_pos, q_start = [], [], []
+        for b, (n, ql) in enumerate(zip(seq_lens, q_lens)):
+            q_start.append(len(tok_row))
+            tok_row += [b] * ql
+            tok_pos += list(range(n - ql, n))
+        self.tok_row, self.tok_pos = i32(tok_row), i32(tok_pos)
+        self.row_q_start, self.row_q_len = i32(q_start), i32(q_lens)
+        self.row_pos_start = i32([n - ql for n, ql in zip(seq_lens, q_lens)])
+        self.row_slot = i32(list(range(B)))
+        self.qcat = torch.cat(self.q).reshape(-1, H * hd).contiguous().to(DEV)
+        self.T = len(tok_row)
+
+    def params(self, out, **kw):
+        return ops().make_attn_params(
+            q=self.qcat, q_stride=self.H * self.hd, out=out, kv=self.kv, block_table=self.bt, tok_row=self.tok_row,
+            tok_pos=self.tok_pos, H=self.H, KV=self.KV, hd=self.hd, ps=self.ps, scale=1.0 / math.sqrt(self.hd),
+            row_slot=self.row_slot, row_q_start=self.row_q_start, row_q_len=self.row_q_len,
+            row_pos_start=self.row_pos_start, **kw)
+
+    def reference(self, window=0, pages=None):
+        """float32 answer; ``pages[b]``: the logical pages row b may read (None: all)."""
+        outs, lses, scores = [], [], []
+        G = self.H // self.KV
+        for b, (n, ql) in enumerate(zip(self.seq_lens, self.q_lens)):
+            k = self.k[b].float().repeat_interleave(G, 1)
+            v = self.v[b].float().repeat_interleave(G, 1)
+            q = self.q[b].float()
+            s = torch.einsum("phd,thd->hpt", q, k) / math.sqrt(self.hd)
+            p_abs = torch.arange(n - ql, n)[:, None]
+            t = torch.arange(n)[None, :]
+            mask = t <= p_abs
+            if window:
+                mask &= t > p_abs - window
+            if pages is not None and pages[b] is not None:
+                allowed = torch.zeros(n, dtype=torch.bool)
+                for lp in pages[b]:
+                    allowed[lp * self.ps:(lp + 1) * self.ps] = True
+                mask &= allowed[None, :]
+            sm = s.masked_fill(~mask[None], float("-inf"))
+            outs.append(torch.einsum("hpt,thd->phd", torch.softmax(sm, -1), v).reshape(ql, -1))
+            lses.append(torch.logsumexp(sm, -1).T)
+            scores.append(s)
+        return torch.cat(outs), torch.cat(lses), scores
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, KV, hd, ps", [(6, 3, 48, 8), (5, 5, 16, 32), (8, 1, 128, 16), (4, 2, 208, 64)])
+def test_attention_plain(dtype, H, KV, hd, ps):
+    o = ops()
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens=[1, 37, 200, 129], q_lens=[1, 5, 64, 2], seed=H)
+    out = torch.empty(case.T, H * hd, dtype=dtype, device=DEV)
+    lse = torch.empty(case.T, H, device=DEV)
+    o.attention_plain(case.params(out, lse=lse))
+    ref, ref_lse, _ = case.reference()
+    assert torch.allclose(out.float().cpu(), ref, **tol(dtype))
+    assert torch.allclose(lse.cpu(), ref_lse, atol=1e-4 if dtype == torch.float32 else 2e-2, rtol=1e-4)
+    # a window whose edge falls inside a page
+    out2 = torch.empty_like(out)
+    o.attention_plain(case.params(out2, window=ps + 3))
+    ref2, _, _ = case.reference(window=ps + 3)
+    assert torch.allclose(out2.float().cpu(), ref2, **tol(dtype))
+
+
+def make_far_key_stand_out(case, b, far, h):
+    """Scales one key so that head h's last query of request b attends to position ``far`` alone."""
+    g = h // (case.H // case.KV)
+    q = case.q[b][-1, h].float()
+    case.k[b][far, g] = (q / q.norm() * 60.0).to(case.dtype)
+    lp, off = far // case.ps, far % case.ps
+    page = int(case.bt[b, lp])
+    case.kv[page, 0, g, off] = case.k[b][far, g].to(DEV)
+
+
+@pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (1, 3, 64, 8), (16, 1, 128, 64), (5, 2, 64, 32), (4, 2, 128, 16)])
+def test_attention_decode_against_plain(G, KV, hd, ps):
+    """The split-key tensor-core kernel against the plain kernel and the float32 answer:
+    contexts from one key to hundreds, ends of pages, a far key that dominates."""
+    o = ops()
+    H = G * KV
+    dtype = torch.bfloat16
+    seq_lens = [1, ps, ps + 1, 63, 64, 65, 400, 1000]
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, [1] * len(seq_lens), seed=G + hd)
+    make_far_key_stand_out(case, 7, 3, H - 1)        # among 1000 keys, the fourth one wins for the last head
+    ref, ref_lse, _ = case.reference()
+    assert ref[7].view(H, hd)[H - 1].sub(case.v[7][3, KV - 1].float()).abs().max() < 1e-3
+    plain = torch.empty(case.T, H * hd, dtype=dtype, device=DEV)
+    o.attention_plain(case.params(plain))
+    for splits in (1, 2, 5, 16):
+        out = torch.empty_like(plain)
+        lse = torch.empty(case.T, H, device=DEV)
+        n = o.attention_decode_scratch_floats(case.T, H, hd, splits)
+        scratch = torch.empty(max(n, 1), device=DEV)
+        p = case.params(out, lse=lse, scratch=scratch, splits=splits)
+        o.attention_decode(p)
+        assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2), f"splits={splits}"
+        assert torch.allclose(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
+        assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+    # a window whose edge lies inside a page, and beyond the first pages
+    out = torch.empty_like(plain)
+    scratch = torch.empty(o.attention_decode_scratch_floats(case.T, H, hd, 3), device=DEV)
+    o.attention_decode(case.params(out, window=ps + 5, scratch=scratch, splits=3))
+    refw, _, _ = case.reference(window=ps + 5)
+    assert torch.allclose(out.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("kernel", ["plain", "decode"])
+def test_attention_on_chosen_pages_and_score_dump(kernel):
+    """Rows flagged for selection read only their chosen pages; a planner's dump holds the
+    scaled scores of every key and the log-sum-exp."""
+    o = ops()
+    H, KV, hd, ps, k = 8, 2, 64, 16, 3
+    dtype = torch.bfloat16
+    seq_lens = [200, 90, 33, 300]
+    B = len(seq_lens)
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, [1] * B, seed=5)
+    flags = i32([1, 1, 0, 1])
+    slots = [2, 0, 3, 1]
+    case.row_slot = i32(slots)
+    sel_pages = torch.zeros(4, k, dtype=torch.int32, device=DEV)
+    sel_count = torch.full((4,), -1, dtype=torch.int32, device=DEV)
+    chosen = {0: [1, 7, 12], 1: None, 2: None, 3: [0, 9, 18]}       # row 1: flagged but reads everything (count -1)
+    for b, pg in chosen.items():
+        if pg is not None:
+            sel_pages[slots[b]] = i32(pg)
+            sel_count[slots[b]] = k
+    run = o.attention_plain if kernel == "plain" else o.attention_decode
+    out = torch.empty(B, H * hd, dtype=dtype, device=DEV)
+    scratch = torch.empty(max(1, o.attention_decode_scratch_floats(B, H, hd, 2)), device=DEV)
+    run(case.params(out, row_flags=flags, sel_pages=sel_pages, sel_count=sel_count, scratch=scratch, splits=2 if kernel == "decode" else 0))
+    ref, _, _ = case.reference(pages=[chosen[b] for b in range(B)])
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    # the dump of a planner layer
+    stride = 304
+    dump = torch.full((B, H, stride), float("nan"), device=DEV)
+    lse = torch.empty(B, H, device=DEV)
+    run(case.params(out, row_flags=flags, dump=dump, lse=lse, scratch=scratch, splits=2 if kernel == "decode" else 0))
+    ref, ref_lse, scores = case.reference()
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    for b, n in enumerate(seq_lens):
+        if b == 2:
+            assert torch.isnan(dump[b]).all()                       # not flagged: nothing is dumped
+        else:
+            assert torch.allclose(dump[b, :, :n].cpu(), scores[b][:, 0, :], atol=2e-2, rtol=2e-2)
+            assert torch.isnan(dump[b, :, n:]).all()
+    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+
+
+# ------------------------------------------------------------------ DELTA
+
+def test_recent_pages_scores_and_selection():
+    from plain_yi import page_scores as plain_scores, select_pages as plain_select
+    o = ops()
+    ps, k, H = 8, 4, 6
+    seqs = [100, 17, 33, 64]          # 13, 3, 5, 8 pages
+    B = len(seqs)
+    flags = i32([1, 1, 1, 0])
+    slots = i32([3, 1, 0, 2])
+    pos_start = i32([n - 1 for n in seqs])
+    q_len = i32([1] * B)
+    q_start = i32(list(range(B)))
+    sel_pages = torch.zeros(4, k, dtype=torch.int32, device=DEV)
+    sel_count = torch.zeros(4, dtype=torch.int32, device=DEV)
+    o.recent_pages(slots, flags, pos_start, q_len, sel_pages, sel_count, ps, 1.0)
+    assert sel_count.tolist() == [k, -1, -1, k]                     # slots 0 (5 pages) and 3 (13 pages) select
+    assert sel_pages[3].tolist() == [9, 10, 11, 12] and sel_pages[0].tolist() == [1, 2, 3, 4]
+    o.recent_pages(slots, flags, pos_start, q_len, sel_pages, sel_count, ps, 1.5)
+    assert sel_count.tolist() == [-1, -1, -1, k]                    # 5 / 4 is below the ratio 1.5
+
+    stride = 104
+    z = torch.randn(B, H, stride, device=DEV) * 2
+    lse = torch.stack([torch.logsumexp(z[b, :, :n], -1) for b, n in enumerate(seqs)])
+    scores = torch.full((B, 16), float("nan"), device=DEV)
+    o.page_scores(z, lse, flags, q_start, pos_start, q_len, scores, ps, k, 1.0)
+    for b, n in enumerate(seqs):
+        npg = (n + ps - 1) // ps
+        if b in (0, 2):
+            want = plain_scores(z[b, :, :n].cpu(), n, ps)
+            assert torch.allclose(scores[b, :npg].cpu(), want, atol=1e-6, rtol=1e-4)
+        else:
+            assert torch.isnan(scores[b]).all()                     # short or unflagged rows are left alone
+    # make ties and a NaN, then select
+    scores[0, 2] = scores[0, 5]
+    scores[2, 0] = float("nan")
+    for keep_last in (1, 2, 4):
+        o.recent_pages(slots, flags, pos_start, q_len, sel_pages, sel_count, ps, 1.0)
+        o.select_pages(scores, slots, flags, pos_start, q_len, sel_pages, sel_count, keep_last, ps, 1e-7, 1.0)
+        for b in (0, 2):
+            npg = (seqs[b] + ps - 1) // ps
+            want = plain_select(scores[b].cpu(), npg, k, keep_last)
+            s = int(slots[b])
+            assert sel_count[s] == k and sel_pages[s].tolist() == want, (keep_last, b)
+
+
+# ------------------------------------------------------------------ sampling
+
+def test_greedy_takes_the_lowest_index_among_equals():
+    o = ops()
+    logits = torch.randn(5, 64000, device=DEV)
+    logits[1, 777] = logits[1, 50000] = 9.0
+    logits[3, 63999] = 11.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    o.sample(logits, out)
+    want = torch.argmax(logits, -1).tolist()
+    want[1] = 777
+    assert out.tolist() == want
+
+
+def test_temperature_and_top_p():
+    from delta_b200.sampling import uniform_of
+    from plain_yi import temperature_probs
+    o = ops()
+    V, R = 1000, 64
+    logits = torch.randn(R, V, device=DEV) * 3
+    temps = torch.full((R,), 0.7, device=DEV)
+    seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 7919
+    pos = torch.arange(R, dtype=torch.int32, device=DEV) + 5
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    o.sample(logits, out, temperature=temps, seeds=seeds, positions=pos)
+    for r in range(R):
+        cdf = torch.cumsum(temperature_probs(logits[r].cpu(), 0.7), 0)
+        u = uniform_of(int(seeds[r]), int(pos[r]))
+        t = int(out[r])
+        assert (cdf[t - 1].item() if t else 0.0) - 1e-5 <= u <= cdf[t].item() + 1e-5
+    # top-p: every draw lies in the kept set of the plain filter, and the draw follows the renormalised distribution
+    top_p = torch.full((R,), 0.6, device=DEV)
+    o.sample(logits, out, temperature=temps, top_p=top_p, seeds=seeds, positions=pos)
+    for r in range(R):
+        probs = temperature_probs(logits[r].cpu(), 0.7, top_p=0.6)
+        t = int(out[r])
+        assert probs[t] > 0
+        cdf = torch.cumsum(probs, 0)
+        u = uniform_of(int(seeds[r]), int(pos[r]))
+        assert (cdf[t - 1].item() if t else 0.0) - 1e-4 <= u <= cdf[t].item() + 1e-4
+    # many draws of one row follow its distribution
+    row = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-30.0] * 12], device=DEV).repeat(4000, 1)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    o.sample(row, out, temperature=torch.ones(4000, device=DEV), seeds=torch.full((4000,), 42, dtype=torch.int64, device=DEV),
+             positions=torch.arange(4000, dtype=torch.int32, device=DEV))
+    freq = torch.bincount(out.long().cpu(), minlength=16)[:4].float() / 4000
+    want = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)
+    assert (freq - want).abs().max() < 0.03
