@@ -93,6 +93,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* kv_smem = smem;                                  // STAGES * 2 * TILE_BYTES
   int* s_key = reinterpret_cast<int*>(smem + STAGES * 2 * TILE_BYTES);  // STAGES * TILE key positions (-1: no key)
+  int* s_lp = s_key + STAGES * TILE;     // logical page of each of this block's entries
+  int* s_page = s_lp + p.reserved;       // its physical page, -1: none (p.reserved = entries a block can have)
 
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
@@ -102,10 +104,31 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
 
   // this block's share of the pages
   const int per = (ri.n_entries + p.splits - 1) / p.splits;
+  if (per > p.reserved) {  // more pages than the block table is wide: a wrong table, not a case to compute
+    if (tid == 0) dk_report(p.err, DK_DEV_BAD_POSITION, ri.t, ri.pos, p.max_pages * p.ps);
+    return;
+  }
   const int e_begin = split * per;
   const int e_end = min(ri.n_entries, e_begin + per);
   const int pages_per_tile = TILE / ps;
   const int n_tiles = e_end > e_begin ? (e_end - e_begin + pages_per_tile - 1) / pages_per_tile : 0;
+
+  // this block's pages: logical and physical ids, looked up once
+  for (int i = tid; i < e_end - e_begin; i += NTHREADS) {
+    const int e = e_begin + i;
+    const int lp = ri.subset ? ri.sel[e] : ri.first_page + e;
+    int page = -1;
+    if (lp >= 0 && lp < p.max_pages) {
+      page = p.block_table[(size_t)row * p.max_pages + lp];
+      if (page < 0 || page >= p.num_pages) {
+        dk_report(p.err, DK_DEV_BAD_PAGE, ri.t, lp, page);
+        page = -1;
+      }
+    }
+    s_lp[i] = lp;
+    s_page[i] = page;
+  }
+  __syncthreads();
 
   // the query heads of this group as A fragments: rows g and g + 8
   uint32_t qa[KB][4];
@@ -128,22 +151,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     for (int i = 0; i < TILE * CHUNKS / NTHREADS; ++i) {
       const int c = tid + i * NTHREADS;
       const int tok = c / CHUNKS, part = c % CHUNKS;
-      const int e = e_begin + tile * pages_per_tile + tok / ps, off = tok % ps;
+      const int el = tile * pages_per_tile + tok / ps, off = tok % ps;
       bool valid = false;
       size_t koff = 0;
       int key = -1;
-      if (e < e_end) {
-        const int lp = ri.subset ? ri.sel[e] : ri.first_page + e;
-        const int k = lp * ps + off;
-        if (lp >= 0 && lp < p.max_pages && k >= ri.lo && k <= ri.pos) {
-          const int page = p.block_table[(size_t)row * p.max_pages + lp];
-          if (page >= 0 && page < p.num_pages) {
-            valid = true;
-            key = k;
-            koff = ((((size_t)page * 2 + 0) * p.KV + kvh) * ps + off) * HD + part * 8;
-          } else if (part == 0) {
-            dk_report(p.err, DK_DEV_BAD_PAGE, ri.t, lp, page);
-          }
+      if (e_begin + el < e_end) {
+        const int page = s_page[el];
+        const int k = s_lp[el] * ps + off;
+        if (page >= 0 && k >= ri.lo && k <= ri.pos) {
+          valid = true;
+          key = k;
+          koff = ((((size_t)page * 2 + 0) * p.KV + kvh) * ps + off) * HD + part * 8;
         }
       }
       const int sw = (part ^ (tok & 7)) * 16;
@@ -348,18 +366,25 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
 }
 
 template <int HD>
-int launch(const DkAttnParams& p, cudaStream_t stream) {
-  constexpr size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int);
+int launch(const DkAttnParams& pin, cudaStream_t stream) {
+  DkAttnParams p = pin;
+  // entries (pages) one block can be given: the widest request split evenly
+  p.reserved = (p.max_pages + p.splits - 1) / p.splits;
+  if (p.reserved > 8192) {
+    dk_set_error("attention_decode: %d pages per block are above the 8192 it keeps in shared memory; use more splits", p.reserved);
+    return DK_ERR_ARG;
+  }
+  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)2 * p.reserved * sizeof(int);
   constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
-  constexpr size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
-  static bool configured = false;
-  if (!configured) {
+  const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+  static size_t configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return DK_ERR_LAUNCH;
     }
-    configured = true;
+    configured = smem;
   }
   dim3 grid(p.splits, p.KV, p.rows);
   attention_decode_kernel<HD><<<grid, NTHREADS, smem, stream>>>(p);

@@ -28,7 +28,14 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
   }
   const T* src = table + (size_t)tok * d;
   T* dst = out + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+  constexpr int VEC = 16 / sizeof(T);
+  if ((d % VEC) == 0) {  // rows start on 16-byte boundaries then
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = threadIdx.x; i < d / VEC; i += blockDim.x) d4[i] = s4[i];
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+  }
 }
 
 extern "C" int dk_embedding(const int* tokens, const void* table, void* out, int T_, int d, int vocab, int dtype,
@@ -81,6 +88,71 @@ __global__ void rms_norm_kernel(T* __restrict__ x, const T* __restrict__ add, co
   }
 }
 
+// The same with 16-byte loads and stores; used when the width is a multiple of the vector
+// length.  Every thread first loads all its vectors, so the loads are in flight together.
+template <typename T, typename W, int MAXV>
+__global__ void rms_norm_vec_kernel(T* __restrict__ x, const T* __restrict__ add, const W* __restrict__ w, T* __restrict__ out,
+                                    const int* __restrict__ rows, int d, float eps, int cast_first) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  const int nvec = d / VEC;
+  uint4* x4 = reinterpret_cast<uint4*>(x + (size_t)s * d);
+  const uint4* a4 = add ? reinterpret_cast<const uint4*>(add + (size_t)s * d) : nullptr;
+  uint4 xv[MAXV], av[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      xv[i] = x4[v];
+      if (a4) av[i] = a4[v];
+    }
+  }
+  float vals[MAXV][VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      const T* xe = reinterpret_cast<const T*>(&xv[i]);
+      const T* ae = reinterpret_cast<const T*>(&av[i]);
+      uint4 st;
+      T* se = reinterpret_cast<T*>(&st);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float f = to_f32<T>(xe[e]);
+        if (a4) {
+          f += to_f32<T>(ae[e]);
+          se[e] = from_f32<T>(f);
+          f = to_f32<T>(se[e]);
+        }
+        vals[i][e] = f;
+        ss += f * f;
+      }
+      if (a4) x4[v] = st;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)d + eps);
+  uint4* o4 = reinterpret_cast<uint4*>(out + (size_t)r * d);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      uint4 st;
+      T* se = reinterpret_cast<T*>(&st);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float n = vals[i][e] * inv;
+        if (cast_first) n = to_f32<T>(from_f32<T>(n));
+        se[e] = from_f32<T>(n * to_f32<W>(w[(size_t)v * VEC + e]));
+      }
+      o4[v] = st;
+    }
+  }
+}
+
 extern "C" int dk_rms_norm(void* x, const void* add, const void* w, void* out, const int* rows, int n_rows, int d,
                            float eps, int dtype, int w_dtype, int cast_first, cudaStream_t stream) {
   if (n_rows == 0) return 0;
@@ -88,8 +160,15 @@ extern "C" int dk_rms_norm(void* x, const void* add, const void* w, void* out, c
   DK_REQUIRE(d <= 12000, "rms_norm: width %d is above the 12000 this kernel keeps in shared memory", d);
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
   const size_t smem = (size_t)(d + 33) * sizeof(float);
-#define LAUNCH(T, W) \
-  rms_norm_kernel<T, W><<<n_rows, threads, smem, stream>>>((T*)x, (const T*)add, (const W*)w, (T*)out, rows, d, eps, cast_first)
+  const int vec = dtype == DK_BF16 ? 8 : 4;
+  const bool use_vec = (d % vec) == 0 && d / vec <= 2 * threads;
+#define LAUNCH(T, W)                                                                                                          \
+  do {                                                                                                                        \
+    if (use_vec)                                                                                                              \
+      rms_norm_vec_kernel<T, W, 2><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)add, (const W*)w, (T*)out, rows, d, eps, cast_first); \
+    else                                                                                                                      \
+      rms_norm_kernel<T, W><<<n_rows, threads, smem, stream>>>((T*)x, (const T*)add, (const W*)w, (T*)out, rows, d, eps, cast_first); \
+  } while (0)
   if (dtype == DK_F32 && w_dtype == DK_F32) LAUNCH(float, float);
   else if (dtype == DK_BF16 && w_dtype == DK_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == DK_BF16 && w_dtype == DK_F32) LAUNCH(__nv_bfloat16, float);
@@ -195,6 +274,71 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
   }
 }
 
+// bfloat16, pairs (j, j + hd/2), head size a multiple of 16: eight pairs per thread with
+// 16-byte loads and stores.
+__global__ void rope_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ tok_pos,
+                                       const int* __restrict__ tok_row, const int* __restrict__ block_table, int max_pages,
+                                       __nv_bfloat16* __restrict__ kv, int num_pages, const float* __restrict__ table,
+                                       int table_positions, int H, int KV, int hd, int ps, int* err) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int b = tok_row[t];
+  const int half = hd / 2, hv = half / 8;          // vectors per half head
+  const size_t stride = (size_t)(H + 2 * KV) * hd;
+  __nv_bfloat16* base = qkv + (size_t)t * stride;
+  if (pos < 0 || (table != nullptr && pos >= table_positions)) {
+    if (threadIdx.x == 0) dk_report(err, DK_DEV_BAD_POSITION, t, pos, table_positions);
+    return;
+  }
+  int page = -1;
+  const int off = pos % ps;
+  if (kv != nullptr) {
+    const int lp = pos / ps;
+    page = lp < max_pages ? block_table[(size_t)b * max_pages + lp] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) dk_report(err, DK_DEV_BAD_PAGE, t, lp, page);
+      page = -1;
+    }
+  }
+  const float4* cs = table ? reinterpret_cast<const float4*>(table + (size_t)pos * half * 2) : nullptr;
+  for (int idx = threadIdx.x; idx < (H + KV) * hv; idx += blockDim.x) {
+    const int hs = idx / hv, jv = idx - hs * hv;
+    __nv_bfloat16* hp = base + (size_t)hs * hd;
+    uint4 av = *reinterpret_cast<const uint4*>(hp + jv * 8);
+    uint4 bv = *reinterpret_cast<const uint4*>(hp + half + jv * 8);
+    if (cs) {
+      __nv_bfloat16* ae = reinterpret_cast<__nv_bfloat16*>(&av);
+      __nv_bfloat16* be = reinterpret_cast<__nv_bfloat16*>(&bv);
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float4 c2 = cs[(jv * 8 + e) / 2];   // cos, sin of pair e and of pair e + 1
+        const float a0 = __bfloat162float(ae[e]), b0 = __bfloat162float(be[e]);
+        const float a1 = __bfloat162float(ae[e + 1]), b1 = __bfloat162float(be[e + 1]);
+        ae[e] = __float2bfloat16_rn(a0 * c2.x - b0 * c2.y);
+        be[e] = __float2bfloat16_rn(a0 * c2.y + b0 * c2.x);
+        ae[e + 1] = __float2bfloat16_rn(a1 * c2.z - b1 * c2.w);
+        be[e + 1] = __float2bfloat16_rn(a1 * c2.w + b1 * c2.z);
+      }
+      *reinterpret_cast<uint4*>(hp + jv * 8) = av;
+      *reinterpret_cast<uint4*>(hp + half + jv * 8) = bv;
+    }
+    if (hs >= H && page >= 0) {
+      __nv_bfloat16* dst = kv + ((((size_t)page * 2 + 0) * KV + (hs - H)) * ps + off) * hd;
+      *reinterpret_cast<uint4*>(dst + jv * 8) = av;
+      *reinterpret_cast<uint4*>(dst + half + jv * 8) = bv;
+    }
+  }
+  if (page >= 0) {
+    const __nv_bfloat16* vsrc = base + (size_t)(H + KV) * hd;
+    const int vv = hd / 8;
+    for (int idx = threadIdx.x; idx < KV * vv; idx += blockDim.x) {
+      const int g = idx / vv, dv = idx - g * vv;
+      *reinterpret_cast<uint4*>(kv + ((((size_t)page * 2 + 1) * KV + g) * ps + off) * hd + dv * 8) =
+          *reinterpret_cast<const uint4*>(vsrc + (size_t)g * hd + dv * 8);
+    }
+  }
+}
+
 extern "C" int dk_rope_append(void* qkv, const int* tok_pos, const int* tok_row, const int* block_table, int max_pages,
                               void* kv, int num_pages, const float* table, int table_positions, int T_, int H, int KV,
                               int hd, int ps, int interleaved, int dtype, int* err, cudaStream_t stream) {
@@ -205,6 +349,12 @@ extern "C" int dk_rope_append(void* qkv, const int* tok_pos, const int* tok_row,
              "rope_append: a cache is given without a block table");
   const int work = (H + KV) * hd / 2;
   const int threads = work >= 2048 ? 256 : 128;
+  if (dtype == DK_BF16 && !interleaved && (hd % 16) == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)kv % 16) == 0) {
+    const int vthreads = work / 8 >= 256 ? 256 : 128;
+    rope_append_vec_kernel<<<T_, vthreads, 0, stream>>>((__nv_bfloat16*)qkv, tok_pos, tok_row, block_table, max_pages,
+                                                        (__nv_bfloat16*)kv, num_pages, table, table_positions, H, KV, hd, ps, err);
+    return dk_check_launch("rope_append");
+  }
 #define LAUNCH(T)                                                                                                   \
   rope_append_kernel<T><<<T_, threads, 0, stream>>>((T*)qkv, tok_pos, tok_row, block_table, max_pages, (T*)kv,      \
                                                      num_pages, table, table_positions, H, KV, hd, ps, interleaved, err)

@@ -32,9 +32,22 @@ __device__ __forceinline__ float uniform_of(unsigned long long seed, int positio
 __device__ int block_argmax(const float* __restrict__ row, int V, float* s_val, int* s_idx, float* out_max) {
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int i = threadIdx.x;
+  // eight loads in flight per thread; indices grow within a thread, so ">" keeps the lowest index
+  for (; i + 7 * (int)blockDim.x < V; i += 8 * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = row[i + u * blockDim.x];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (v[u] > best) {
+        best = v[u];
+        bi = i + u * blockDim.x;
+      }
+  }
+  for (; i < V; i += blockDim.x) {
     const float v = row[i];
-    if (v > best || (v == best && i < bi)) {
+    if (v > best) {
       best = v;
       bi = i;
     }

@@ -12,13 +12,14 @@ from ..kernels import ops
 
 SM_COUNT = 148
 DECODE_TILE = 64
-MAX_SPLITS = 32
+MAX_SPLITS = 64
+BLOCKS_PER_SM = 2     # the decode kernel's registers and shared memory let two blocks share an SM
 
 
 def decode_splits(rows: int, kv_heads: int, max_keys: int) -> int:
-    """Blocks per (row, key-value head): enough to fill the GPU twice over, no more than
-    there are 64-key tiles."""
-    want = -(-2 * SM_COUNT // max(1, rows * kv_heads))
+    """Blocks per (row, key-value head): as many as run at once (a second, partly filled
+    wave would double the time), no more than there are 64-key tiles."""
+    want = (BLOCKS_PER_SM * SM_COUNT) // max(1, rows * kv_heads)
     tiles = max(1, -(-max_keys // DECODE_TILE))
     return max(1, min(want, tiles, MAX_SPLITS))
 

@@ -34,6 +34,7 @@ class StepContext:
         self.row_q_len = sections["row_q_len"]
         self.row_pos_start = sections["row_pos_start"]
         self.logit_rows = sections["logit_rows"]
+        self.sampling_sections = {k: v for k, v in sections.items() if k.startswith("samp_")}
         self.block_tables = block_tables
         self.host = host
         self.num_tokens = int(self.tokens.shape[0])

@@ -49,6 +49,7 @@ class LMBackend:
         self.tokenizer = None
         self.step_timings: List[dict] = []
         self.throughput_mode = False
+        self._host_tokens = None
         self.record_timings = False
 
     # ---- set-up -------------------------------------------------------------
@@ -120,23 +121,19 @@ class LMBackend:
                 return [r]
             return []
         rows = []
-        samp, positions = [], []
         for x in plan:
             r = x.request
             toks = r.tokens[x.start:x.start + x.count]
             rows.append(RowInput(r.slot, toks, x.start, [x.count - 1] if x.samples else [],
-                                 selective=bool(sch.selective and x.decode)))
-            if x.samples:
-                samp.append(r.sampling)
-                positions.append(x.start + x.count)
+                                 selective=bool(sch.selective and x.decode), sampling=r.sampling))
         ev = None
         if self.record_timings:
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             ev[0].record()
-        logits = runner.step(rows)
+        logits, tokens = runner.step_and_sample(rows)
         if ev:
             ev[1].record()
-        new_tokens = sample(logits, samp, positions).tolist() if samp else []
+        new_tokens = self._to_host(tokens)
         if ev:
             ev[2].record()
             torch.cuda.synchronize()
@@ -146,6 +143,17 @@ class LMBackend:
                                           active_bsz=len(rows), tokens=sum(x.count for x in plan),
                                           total_pages=sum(runner.cache.pages_in_use().values())))
         return sch.complete(plan, new_tokens)
+
+    def _to_host(self, tokens: torch.Tensor) -> List[int]:
+        """The device-to-host read of a step's result, through pinned memory."""
+        n = tokens.shape[0]
+        if n == 0:
+            return []
+        if self._host_tokens is None or self._host_tokens.numel() < n:
+            self._host_tokens = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+        self._host_tokens[:n].copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._host_tokens[:n].tolist()
 
     def run_scheduler_loop(self) -> List[dict]:
         """Runs until every request is finished (or, in throughput mode, until the first one

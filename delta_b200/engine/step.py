@@ -40,6 +40,7 @@ class RowInput:
     start_pos: int
     want: Sequence[int] = ()
     selective: bool = False   # a decode token that DELTA's page selection applies to
+    sampling: Optional[object] = None   # SamplingParams for the tokens sampled at ``want`` (None: greedy)
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -103,6 +104,9 @@ class ModelRunner:
         self.capture: Optional[dict] = None
         self.steps_run = 0
         self.last_staging_bytes = 0
+        self._graphs: Dict[int, dict] = {}
+        self.graph_captures = 0
+        self.graph_replays = 0
 
     # ---- staging ---------------------------------------------------------------
     def _pinned(self, n: int):
@@ -118,20 +122,30 @@ class ModelRunner:
             self._staging[i][0] = buf
         return i, buf
 
-    def build_context(self, rows: List[RowInput]) -> StepContext:
-        """Fills the staging buffer for these rows and copies it to the device."""
-        B = len(rows)
+    def _layout(self, B: int, T: int, R: int, max_pages: int):
+        """Where each section of a step's metadata lies in the staging buffer (in ints)."""
+        layout = {}
+        pos = 0
+        for key, n in (("tokens", T), ("tok_row", T), ("tok_pos", T), ("row_slot", B), ("row_flags", B), ("row_q_start", B),
+                       ("row_q_len", B), ("row_pos_start", B), ("logit_rows", R), ("samp_temp", R), ("samp_top_p", R),
+                       ("samp_pos", R), ("samp_seed", 2 * R)):
+            layout[key] = (pos, n)
+            pos = _align(pos + n)
+        for g in self.cache.groups:
+            layout["bt:" + g] = (pos, B * max_pages)
+            pos = _align(pos + B * max_pages)
+        return layout, pos
+
+    def _check_rows(self, rows: List[RowInput]):
         q_lens = [len(r.tokens) for r in rows]
-        T = sum(q_lens)
-        wants = []
-        q_start = []
-        off = 0
-        max_seq = 0
+        wants, q_start, off, max_seq = [], [], 0, 0
         for r, n in zip(rows, q_lens):
             if n < 1:
                 raise ValueError("a row of a step needs at least one token")
             if not self.cache.is_live(r.slot):
                 raise ValueError(f"slot {r.slot} is not live")
+            if r.selective and n != 1:
+                raise ValueError("page selection applies to single decode tokens only")
             for w in r.want:
                 if not (0 <= w < n):
                     raise ValueError(f"wanted place {w} lies outside the row's {n} tokens")
@@ -143,48 +157,49 @@ class ModelRunner:
             for g in self.cache.groups.values():
                 if int(g.num_logical[r.slot]) * g.page_size < end:
                     raise ValueError(f"slot {r.slot} has no pages for {end} tokens; grow it before the step")
-        if len(set(r.slot for r in rows)) != B:
+        if len(set(r.slot for r in rows)) != len(rows):
             raise ValueError("a request appears twice in one step")
-        R = len(wants)
-        max_pages = max(1, _align((max_seq + self.cache.page_size - 1) // self.cache.page_size))
-        max_pages = min(max_pages, self.cache.max_pages_per_request) if self.cache.max_pages_per_request >= 1 else max_pages
-        names = list(self.cache.groups)
-        layout = {}
-        pos = 0
-        for key, n in (("tokens", T), ("tok_row", T), ("tok_pos", T), ("row_slot", B), ("row_flags", B), ("row_q_start", B),
-                       ("row_q_len", B), ("row_pos_start", B), ("logit_rows", R)):
-            layout[key] = (pos, n)
-            pos = _align(pos + n)
-        for g in names:
-            layout["bt:" + g] = (pos, B * max_pages)
-            pos = _align(pos + B * max_pages)
-        idx, pinned = self._pinned(pos)
-        host = pinned.numpy()
+        return q_lens, q_start, wants, max_seq
+
+    def _fill(self, host: np.ndarray, layout: dict, rows: List[RowInput], q_lens, q_start, wants, max_pages: int) -> None:
+        B = len(rows)
 
         def put(key, values):
             a, n = layout[key]
             host[a:a + n] = values
 
-        if T:
-            put("tokens", np.concatenate([np.asarray(r.tokens, dtype=np.int32) for r in rows]))
-            put("tok_row", np.repeat(np.arange(B, dtype=np.int32), q_lens))
-            put("tok_pos", np.concatenate([np.arange(r.start_pos, r.start_pos + n, dtype=np.int32) for r, n in zip(rows, q_lens)]))
+        put("tokens", np.concatenate([np.asarray(r.tokens, dtype=np.int32) for r in rows]))
+        put("tok_row", np.repeat(np.arange(B, dtype=np.int32), q_lens))
+        put("tok_pos", np.concatenate([np.arange(r.start_pos, r.start_pos + n, dtype=np.int32) for r, n in zip(rows, q_lens)]))
         put("row_slot", [r.slot for r in rows])
         put("row_flags", [1 if r.selective else 0 for r in rows])
         put("row_q_start", q_start)
         put("row_q_len", q_lens)
         put("row_pos_start", [r.start_pos for r in rows])
         put("logit_rows", wants)
+        if wants:
+            temp, top_p, pos, seed = [], [], [], []
+            for r in rows:
+                sp = r.sampling
+                for w in r.want:
+                    temp.append(sp.temperature if sp else 0.0)
+                    top_p.append(sp.top_p if sp else 1.0)
+                    seed.append((sp.seed if sp else 0) & 0xFFFFFFFFFFFFFFFF)
+                    pos.append(r.start_pos + w + 1)     # the position the new token will take
+            put("samp_temp", np.asarray(temp, dtype=np.float32).view(np.int32))
+            put("samp_top_p", np.asarray(top_p, dtype=np.float32).view(np.int32))
+            put("samp_pos", pos)
+            put("samp_seed", np.asarray(seed, dtype=np.uint64).view(np.int32))
         slots = [r.slot for r in rows]
-        for g in names:
+        for g in self.cache.groups:
             a, n = layout["bt:" + g]
             host[a:a + n] = self.cache.groups[g].table[slots, :max_pages].reshape(-1)
-        self.last_staging_bytes = pos * 4
-        dev = torch.empty(pos, dtype=torch.int32, device=self.device)
-        dev.copy_(pinned[:pos], non_blocking=True)
-        self._staging[idx][1] = _record_event()
+
+    def _context(self, dev: torch.Tensor, layout: dict, rows, q_lens, q_start, wants, max_pages, max_seq) -> StepContext:
+        B = len(rows)
         sections = {k: dev[a:a + n] for k, (a, n) in layout.items() if not k.startswith("bt:")}
-        block_tables = {g: dev[layout["bt:" + g][0]:layout["bt:" + g][0] + B * max_pages].view(B, max_pages) for g in names}
+        block_tables = {g: dev[layout["bt:" + g][0]:layout["bt:" + g][0] + B * max_pages].view(B, max_pages)
+                        for g in self.cache.groups}
         info = dict(max_pages=max_pages, any_selective=any(r.selective for r in rows),
                     decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens) if q_lens else 0, max_seq_len=max_seq,
                     rows=rows, q_lens=q_lens, q_start=q_start, wants=wants)
@@ -192,15 +207,26 @@ class ModelRunner:
                            block_tables=block_tables, host=info, err=self.err, scratch_pool=self._scratch,
                            plain_products=self.plain_products, plain_attention=self.plain_attention, capture=self.capture)
 
+    def build_context(self, rows: List[RowInput]) -> StepContext:
+        """Fills the staging buffer for these rows and copies it to the device."""
+        q_lens, q_start, wants, max_seq = self._check_rows(rows)
+        ps = self.cache.page_size
+        max_pages = min(max(1, _align((max_seq + ps - 1) // ps)), max(1, self.cache.max_pages_per_request))
+        layout, size = self._layout(len(rows), sum(q_lens), len(wants), max_pages)
+        idx, pinned = self._pinned(size)
+        self._fill(pinned.numpy(), layout, rows, q_lens, q_start, wants, max_pages)
+        self.last_staging_bytes = size * 4
+        dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        dev.copy_(pinned[:size], non_blocking=True)
+        self._staging[idx][1] = _record_event()
+        return self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, max_seq)
+
     # ---- the step ----------------------------------------------------------------
     def step(self, rows: List[RowInput]) -> torch.Tensor:
         """Runs one batch.  Pages for the new tokens must be held already
         (``cache.grow``); afterwards the caller records the new lengths
         (``cache.advance``).  Returns float32 logits [wanted places, vocab] on the
         device, in the order of the rows and of their ``want`` lists."""
-        for r in rows:
-            if r.selective and len(r.tokens) != 1:
-                raise ValueError("page selection applies to single decode tokens only")
         if not rows:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         ctx = self.build_context(rows)
@@ -209,6 +235,92 @@ class ModelRunner:
         if self.cfg.check_kernel_errors:
             ops.raise_if_error(self.err)
         return logits
+
+    def _sample(self, ctx: StepContext, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        R = logits.shape[0]
+        out = out if out is not None else torch.empty(R, dtype=torch.int32, device=self.device)
+        if R:
+            s = ctx.sampling_sections
+            ops.sample(logits, out, temperature=s["samp_temp"].view(torch.float32), top_p=s["samp_top_p"].view(torch.float32),
+                       seeds=s["samp_seed"].view(torch.int64), positions=s["samp_pos"])
+        return out
+
+    def step_and_sample(self, rows: List[RowInput]):
+        """One batch, and one new token for every wanted place (greedy, or as the row's
+        ``sampling`` says).  Returns (logits, tokens), both on the device.  A step in which
+        every row brings one token is replayed from a CUDA graph when the engine was set up
+        with ``cuda_graph_decode``."""
+        if not rows:
+            return (torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device),
+                    torch.empty(0, dtype=torch.int32, device=self.device))
+        if self.cfg.cuda_graph_decode and all(len(r.tokens) == 1 and list(r.want) == [0] for r in rows):
+            return self._graph_step(rows)
+        ctx = self.build_context(rows)
+        logits = self.model.forward(ctx)
+        tokens = self._sample(ctx, logits)
+        self.steps_run += 1
+        if self.cfg.check_kernel_errors:
+            ops.raise_if_error(self.err)
+        return logits, tokens
+
+    # ---- decode steps from a CUDA graph ---------------------------------------------
+    def _graph_step(self, rows: List[RowInput]):
+        """Replays the captured decode step for this batch size.  All metadata lives in one
+        device buffer of fixed layout that a single copy refreshes before the replay; block
+        tables have their full width, the attention grid is the one sized for the longest
+        request the engine allows, so nothing in the graph depends on the step.
+        Reference: backend.py:974-1001 (when a graph is used), 1119-1162 (two warm-up runs,
+        then capture)."""
+        from .attention_dispatch import decode_splits
+        B = len(rows)
+        q_lens, q_start, wants, max_seq = self._check_rows(rows)
+        max_pages = self.cache.max_pages_per_request
+        g = self._graphs.get(B)
+        if g is None:
+            layout, size = self._layout(B, B, B, max_pages)
+            g = dict(layout=layout, size=size, dev=torch.zeros(size, dtype=torch.int32, device=self.device), graph=None,
+                     warm=0)
+            self._graphs[B] = g
+        layout, size, dev = g["layout"], g["size"], g["dev"]
+        idx, pinned = self._pinned(size)
+        self._fill(pinned.numpy(), layout, rows, q_lens, q_start, wants, max_pages)
+        self.last_staging_bytes = size * 4
+        dev.copy_(pinned[:size], non_blocking=True)
+        self._staging[idx][1] = _record_event()
+
+        def run():
+            ctx = self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, self.cache.max_seq_len)
+            ctx.any_selective = self.cfg.selective is not None
+            ctx.capture = None
+            kvh = max((cs.kv_heads for cs in self.model.cache_specs().values()), default=1)
+            ctx.fixed_decode_splits = decode_splits(B, kvh, self.cache.max_seq_len)
+            logits = self.model.forward(ctx)
+            tokens = self._sample(ctx, logits)
+            return logits, tokens
+
+        if g["graph"] is None:
+            if g["warm"] < 2:           # eager runs first: they size every scratch buffer
+                g["warm"] += 1
+                out = run()
+                self.steps_run += 1
+                return out
+            # the eager runs have sized the scratch buffers; now record the same launches
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            l0 = ops.launch_count()
+            with torch.cuda.graph(graph):
+                g["out"] = run()
+            g["graph"] = graph
+            g["launches"] = ops.launch_count() - l0     # kernels recorded, not run
+            ops.count_launch(-g["launches"])
+            self.graph_captures += 1
+        g["graph"].replay()
+        ops.count_launch(g["launches"])
+        self.steps_run += 1
+        self.graph_replays += 1
+        if self.cfg.check_kernel_errors:
+            ops.raise_if_error(self.err)
+        return g["out"]
 
     # ---- convenience used by replay and tests --------------------------------------
     def run_rows(self, rows: List[RowInput]) -> torch.Tensor:

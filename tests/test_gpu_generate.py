@@ -121,3 +121,28 @@ def test_command_line(model_folders, tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     res = json.loads(out.read_text())
     assert res["summary"]["generated_tokens"] == 30 and len(res["results"]) == 5
+
+
+@pytest.mark.parametrize("selective", [False, True])
+def test_cuda_graph_decode_gives_the_same_tokens(model_folders, selective):
+    """Decode steps replayed from a CUDA graph generate what eager steps generate, with
+    batches that shrink as requests finish (one graph per batch size) and with DELTA on."""
+    from delta_b200.engine import LMBackend
+    folder = model_folders["B"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(n, plain.cfg.vocab, 80 + i) for i, n in enumerate([30, 9, 50, 17])]
+    outs = {}
+    for graphs in (False, True):
+        e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=graphs)
+        e.load_model(folder)
+        e.setup_caches(max_batch_size=4, max_seq_length=128, page_size=8, check_kernel_errors=True,
+                       enable_selective_cache=selective, full_cache_layers=[1], subset_cache_size=4, L=2)
+        first = len(e.scheduler.requests)
+        e.add_requests(prompts, [60, 40, 90, 128], [])
+        e.run_scheduler_loop()
+        outs[graphs] = [r.output for r in e.scheduler.requests[first:]]
+        if graphs:
+            assert e.runner.graph_captures >= 2 and e.runner.graph_replays > 20
+    assert outs[True] == outs[False]
+    if not selective:
+        assert outs[True][1] == plain_greedy(plain, prompts[1], 31)
