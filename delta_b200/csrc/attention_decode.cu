@@ -19,38 +19,13 @@
 // page scoring (reference: backend.py:191-221, 562-577).
 #include "common.cuh"
 #include "attention_params.h"
+#include "mma_helpers.cuh"
 
 namespace {
 constexpr int TILE = 64;     // keys per tile
 constexpr int STAGES = 3;
 constexpr int NWARPS = 4;
 constexpr int NTHREADS = NWARPS * 32;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-  const int sz = valid ? 16 : 0;  // size 0: the 16 bytes are filled with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 struct RowInfo {
   int t, pos, lo, slot, n_entries, first_page;
@@ -94,17 +69,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   unsigned char* kv_smem = smem;                                  // STAGES * 2 * TILE_BYTES
   int* s_key = reinterpret_cast<int*>(smem + STAGES * 2 * TILE_BYTES);  // STAGES * TILE key positions (-1: no key)
   int* s_lp = s_key + STAGES * TILE;     // logical page of each of this block's entries
-  int* s_page = s_lp + p.reserved;       // its physical page, -1: none (p.reserved = entries a block can have)
+  int* s_page = s_lp + p.block_entries;       // its physical page, -1: none (p.block_entries = entries a block can have)
 
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int G = p.H / p.KV, ps = p.ps;
+  if (p.row_filter == 1 && p.row_q_len[row] != 1) return;   // a row of a prompt: the prefill kernel's
   const RowInfo ri = row_info(p, row);
   const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(p.kv);
 
   // this block's share of the pages
   const int per = (ri.n_entries + p.splits - 1) / p.splits;
-  if (per > p.reserved) {  // more pages than the block table is wide: a wrong table, not a case to compute
+  if (per > p.block_entries) {  // more pages than the block table is wide: a wrong table, not a case to compute
     if (tid == 0) dk_report(p.err, DK_DEV_BAD_POSITION, ri.t, ri.pos, p.max_pages * p.ps);
     return;
   }
@@ -347,6 +323,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
 template <int HD>
 __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   const int row = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  if (p.row_filter == 1 && p.row_q_len[row] != 1) return;
   const float* sc = reinterpret_cast<const float*>(p.scratch);
   const int t = p.row_q_start[row] + p.row_q_len[row] - 1;
   float M = -INFINITY;
@@ -369,12 +346,12 @@ template <int HD>
 int launch(const DkAttnParams& pin, cudaStream_t stream) {
   DkAttnParams p = pin;
   // entries (pages) one block can be given: the widest request split evenly
-  p.reserved = (p.max_pages + p.splits - 1) / p.splits;
-  if (p.reserved > 8192) {
-    dk_set_error("attention_decode: %d pages per block are above the 8192 it keeps in shared memory; use more splits", p.reserved);
+  p.block_entries = (p.max_pages + p.splits - 1) / p.splits;
+  if (p.block_entries > 8192) {
+    dk_set_error("attention_decode: %d pages per block are above the 8192 it keeps in shared memory; use more splits", p.block_entries);
     return DK_ERR_ARG;
   }
-  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)2 * p.reserved * sizeof(int);
+  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)2 * p.block_entries * sizeof(int);
   constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
   const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
   static size_t configured = 0;
@@ -417,7 +394,8 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
   DK_REQUIRE(dk_attention_decode_supported(p.dtype, p.H, p.KV, p.hd, p.ps),
              "attention_decode: sizes not taken (bfloat16, head size 64 or 128, at most 16 query heads per key-value head, "
              "page size a power of two <= 64): dtype=%d H=%d KV=%d hd=%d ps=%d", p.dtype, p.H, p.KV, p.hd, p.ps);
-  DK_REQUIRE(p.T == p.rows, "attention_decode: %d tokens for %d rows; every row must bring one token", p.T, p.rows);
+  DK_REQUIRE(p.T == p.rows || p.row_filter == 1,
+             "attention_decode: %d tokens for %d rows; every row must bring one token unless rows are filtered", p.T, p.rows);
   DK_REQUIRE(p.row_q_start != nullptr && p.row_q_len != nullptr, "attention_decode: row_q_start / row_q_len are missing");
   DK_REQUIRE(p.splits >= 1 && p.splits <= 65535 && p.KV <= 65535 && p.rows <= 65535, "attention_decode: grid too large");
   DK_REQUIRE(p.splits == 1 || p.scratch != nullptr, "attention_decode: %d splits need a scratch buffer", p.splits);

@@ -24,5 +24,7 @@ struct DkAttnParams {
   int T, rows, H, KV, hd, ps, max_pages, num_pages;
   int q_stride, window, sel_stride, dump_stride, dtype, splits;
   float scale;
+  int block_entries;       // set by the launchers: pages one block keeps in shared memory
+  int row_filter;          // 0: every row; 1: only rows that bring one token; 2: only rows that bring more
   int reserved;
 };

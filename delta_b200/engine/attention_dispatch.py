@@ -1,8 +1,9 @@
-"""Chooses the attention kernel for a batch.
+"""Chooses the attention kernels for a batch.
 
-Steps in which every row brings one token go to the split-key decode kernel when it
-takes the sizes (bfloat16, head size 64 or 128, at most 16 query heads per key-value
-head); everything else goes to the plain kernel, which takes every size.
+bfloat16 with head size 64 or 128: rows that bring one token go to the split-key decode
+kernel (at most 16 query heads per key-value head), rows that bring more go to the tiled
+prefill kernel; a mixed step launches both, each skipping the other's rows.  Everything
+else (32 bit, other head sizes) goes to the plain kernel, which takes every size.
 """
 from __future__ import annotations
 
@@ -24,18 +25,42 @@ def decode_splits(rows: int, kv_heads: int, max_keys: int) -> int:
     return max(1, min(want, tiles, MAX_SPLITS))
 
 
+def _decode(ctx, params, row_filter: int) -> None:
+    max_keys = ctx.max_seq_len if not params.window else min(ctx.max_seq_len, params.window + params.ps)
+    splits = ctx.fixed_decode_splits or decode_splits(ctx.num_rows, params.KV, max_keys)
+    params.splits = splits
+    params.row_filter = row_filter
+    if splits > 1:
+        n = ops.attention_decode_scratch_floats(ctx.num_rows, params.H, params.hd, splits)
+        params.scratch = ctx.scratch("attention.decode_partials", (n,), torch.float32).data_ptr()
+    ops.attention_decode(params)
+
+
 def run(ctx, params) -> None:
-    if (ctx.decode_only and not ctx.plain_attention
-            and ops.attention_decode_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)):
-        max_keys = ctx.max_seq_len if not params.window else min(ctx.max_seq_len, params.window + params.ps)
-        if params.sel_pages is not None and not params.dump:
-            pass  # chosen pages bound the keys too, but rows that read everything may share the step
-        splits = ctx.fixed_decode_splits or decode_splits(ctx.num_rows, params.KV, max_keys)
-        params.splits = splits
-        if splits > 1:
-            n = ops.attention_decode_scratch_floats(ctx.num_rows, params.H, params.hd, splits)
-            scratch = ctx.scratch("attention.decode_partials", (n,), torch.float32)
-            params.scratch = scratch.data_ptr()
-        ops.attention_decode(params)
+    if ctx.plain_attention or ctx.dtype != torch.bfloat16:
+        ops.attention_plain(params)
         return
-    ops.attention_plain(params)
+    dec_ok = ops.attention_decode_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)
+    pre_ok = ops.attention_prefill_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)
+    if ctx.decode_only:
+        if dec_ok:
+            _decode(ctx, params, 0)
+        else:
+            ops.attention_plain(params)
+        return
+    if not pre_ok:
+        ops.attention_plain(params)
+        return
+    singles = any(n == 1 for n in ctx.host["q_lens"])
+    if not singles:
+        params.row_filter = 0
+        ops.attention_prefill(params, ctx.max_q_len)
+    elif dec_ok:
+        _decode(ctx, params, 1)
+        params.row_filter = 2
+        ops.attention_prefill(params, ctx.max_q_len)
+    elif params.sel_pages is None and params.dump is None:
+        params.row_filter = 0
+        ops.attention_prefill(params, ctx.max_q_len)
+    else:
+        ops.attention_plain(params)

@@ -32,7 +32,7 @@ class AttnParams(C.Structure):
         ("sel_pages", P), ("sel_count", P), ("dump", P), ("lse", P), ("scratch", P), ("err", P),
         ("T", I), ("rows", I), ("H", I), ("KV", I), ("hd", I), ("ps", I), ("max_pages", I), ("num_pages", I),
         ("q_stride", I), ("window", I), ("sel_stride", I), ("dump_stride", I), ("dtype", I), ("splits", I),
-        ("scale", F), ("reserved", I),
+        ("scale", F), ("block_entries", I), ("row_filter", I), ("reserved", I),
     ]
 
 
@@ -50,6 +50,8 @@ _SIGNATURES = {
     "dk_sample": [P, I, I, I, P, P, P, P, P, P, P],
     "dk_attention_decode": [C.POINTER(AttnParams), P],
     "dk_attention_decode_supported": [I, I, I, I, I],
+    "dk_attention_prefill": [C.POINTER(AttnParams), I, P],
+    "dk_attention_prefill_supported": [I, I, I, I, I],
     "dk_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_gemm_small_m_supported": [I, I, I, I],
 }

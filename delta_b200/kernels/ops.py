@@ -137,7 +137,7 @@ def gemm_nt_plain(a, w, out):
 
 def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, KV, hd, ps, scale, row_slot=None,
                      row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None, sel_pages=None,
-                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0) -> AttnParams:
+                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0, row_filter=0) -> AttnParams:
     p = AttnParams()
     i32 = torch.int32
     p.q = _ptr(q, "q")
@@ -170,6 +170,7 @@ def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, 
     p.dump_stride = dump.shape[-1] if dump is not None else 0
     p.dtype = dtype_code(q.dtype)
     p.splits = splits
+    p.row_filter = row_filter
     p.scale = float(scale)
     return p
 
@@ -192,6 +193,18 @@ def attention_decode(params: AttnParams):
     """One new token per row; ``params.splits`` blocks share a request's keys and, when there
     is more than one, ``params.scratch`` holds their partial results."""
     _l.check(_l.load().dk_attention_decode(C.byref(params), _stream()), "attention_decode", 2 if params.splits > 1 else 1)
+
+
+def attention_prefill_supported(dtype, H, KV, hd, ps) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_l.load().dk_attention_prefill_supported(BF16, H, KV, hd, ps))
+
+
+def attention_prefill(params: AttnParams, max_q_len: int):
+    """Rows that bring several tokens (``params.row_filter`` 2 leaves single tokens to the
+    decode kernel); ``max_q_len`` is the most tokens any row brings."""
+    _l.check(_l.load().dk_attention_prefill(C.byref(params), int(max_q_len), _stream()), "attention_prefill")
 
 
 def gemm_small_m_supported(M, N, K, swiglu=False) -> bool:

@@ -30,4 +30,4 @@ def model_folders(tmp_path_factory):
     import torch
     import helpers
     root = tmp_path_factory.mktemp("models")
-    return {w: helpers.make_model_folder(root, w, torch.float32) for w in ("A", "B", "C")}
+    return {w: helpers.make_model_folder(root, w, torch.float32) for w in ("A", "B", "C", "D")}

@@ -27,11 +27,15 @@ def tiny_config(which: str) -> dict:
                     intermediate_size=200, vocab_size=777, rope_theta=250000.0, rms_norm_eps=3e-6,
                     max_position_embeddings=384, sliding_window=24,
                     layer_types=["full_attention", "sliding_attention", "full_attention", "sliding_attention"])
+    if which == "D":  # head size 64: the sizes the tensor-core attention kernels take
+        return dict(base, hidden_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+                    intermediate_size=208, vocab_size=384, rope_theta=1000000.0, rms_norm_eps=1e-5,
+                    max_position_embeddings=512)
     raise KeyError(which)
 
 
-PAGE_SIZE = {"A": 16, "B": 8, "C": 32}
-SEED = {"A": 0, "B": 1, "C": 2}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 32, "D": 16}
+SEED = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 def make_model_folder(tmp_path, which: str, dtype=torch.float32) -> Path:

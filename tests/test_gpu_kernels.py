@@ -310,6 +310,40 @@ def test_attention_decode_against_plain(G, KV, hd, ps):
     assert torch.allclose(out.float().cpu(), refw, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H, KV, hd, ps", [(8, 2, 128, 16), (3, 3, 64, 8), (4, 1, 64, 64), (32, 4, 128, 32)])
+def test_attention_prefill_against_plain(H, KV, hd, ps):
+    """The tiled tensor-core prefill kernel: whole prompts, portions that start inside a page,
+    tiles that end before a page does, single tokens left to the decode kernel."""
+    o = ops()
+    dtype = torch.bfloat16
+    seq_lens = [200, 129, 64, 300, 1000, 65, 1]
+    q_lens = [200, 5, 64, 2, 37, 1, 1]
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, q_lens, seed=H + ps)
+    make_far_key_stand_out(case, 4, 2, 0)            # the last query of request 4 looks far back
+    ref, ref_lse, _ = case.reference()
+    out = torch.zeros(case.T, H * hd, dtype=dtype, device=DEV)
+    lse = torch.zeros(case.T, H, device=DEV)
+    o.attention_prefill(case.params(out, lse=lse), max(q_lens))
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+    # single tokens are skipped with row_filter 2 and taken by the decode kernel with row_filter 1
+    out2 = torch.zeros_like(out)
+    o.attention_prefill(case.params(out2, row_filter=2), max(q_lens))
+    singles = [sum(q_lens[:5]), sum(q_lens[:6])]
+    assert out2[singles].abs().sum() == 0
+    if H // KV <= 16:
+        scratch = torch.empty(o.attention_decode_scratch_floats(len(seq_lens), H, hd, 2), device=DEV)
+        o.attention_decode(case.params(out2, row_filter=1, scratch=scratch, splits=2))
+    else:
+        out2[singles] = out[singles]
+    assert torch.allclose(out2.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    # a window whose edge lies inside a tile and inside a page
+    out3 = torch.zeros_like(out)
+    o.attention_prefill(case.params(out3, window=ps + 7), max(q_lens))
+    refw, _, _ = case.reference(window=ps + 7)
+    assert torch.allclose(out3.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("kernel", ["plain", "decode"])
 def test_attention_on_chosen_pages_and_score_dump(kernel):
     """Rows flagged for selection read only their chosen pages; a planner's dump holds the

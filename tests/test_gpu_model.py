@@ -10,7 +10,7 @@ from plain_yi import PlainYi
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 90], "B": [1, 9, 40, 100], "C": [3, 50, 75, 120]}
+LENGTHS = {"A": [5, 17, 33, 90], "B": [1, 9, 40, 100], "C": [3, 50, 75, 120], "D": [2, 70, 131, 200]}
 # tolerances: float32 against a float32 plain implementation differs by rounding of sums in
 # another order (about 1e-6 of logits below 2); bfloat16 against the plain implementation
 # that rounds to bfloat16 at the same places differs by single roundings that flip.
@@ -45,7 +45,7 @@ def compare(results, refs, lengths, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 def test_every_way_of_cutting(model_folders, which, dtype):
     folder = model_folders[which]
     lengths = LENGTHS[which]

@@ -16,6 +16,7 @@ CASES = [
     ("A", (0,), 2, 1, 1.5),      # selection starts only when pages / k > 1.5
     ("C", (0,), 2, 1, 1.0),      # layer 0 plans for layer 2; the windowed layers 1 and 3 take no selection
     ("B", (0, 1), 2, 2, 1.0),    # two full layers, the second one plans
+    ("D", (0,), 3, 2, 1.0),      # head size 64: the tensor-core decode kernel dumps, scores and reads chosen pages
 ]
 
 
