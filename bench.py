@@ -48,7 +48,7 @@ def peaks() -> dict:
     if p.is_file():
         try:
             d = json.loads(p.read_text())
-            out = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+            out = dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
                        source="measured")
             return out
         except Exception:  # noqa: BLE001
@@ -237,6 +237,10 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
         "points": points,
     }
+    from delta_b200.parts import linear
+    print("kernels chosen per product (rows bucket, N, K, swiglu, out): " +
+          "; ".join(f"{k[0]}x{k[1]}x{k[2]}{'sw' if k[3] else ''}->{v}" for k, v in sorted(linear.choices().items(), key=str)),
+          file=sys.stderr)
     print(json.dumps(out))
     return 0
 

@@ -1,0 +1,365 @@
+// y[M,N] = x[M,K] W[N,K]^T on the fifth-generation tensor cores, for decode steps (M up to
+// 128 rows): the weights stream once through shared memory by TMA and never touch
+// registers.
+//
+// "Swap AB": a block owns 128 rows of W, which are the M side of a tcgen05.mma tile
+// (A operand), and all M activation rows, padded to a multiple of 16, are its N side (B
+// operand).  The accumulator D[128 x Mpad] lives in tensor memory (TMEM).
+//
+//   thread 0        producer: per stage up to four TMA boxes [128 x 64] of W (512 contiguous
+//                   bytes of every weight row are asked for together, which the memory
+//                   likes far better than 128) and as many boxes [Mpad x 64] of x, into a
+//                   ring of shared-memory stages (128-byte swizzle), signalled by mbarrier
+//                   transaction counts
+//   thread 32       issues four tcgen05.mma (K = 16 each) per box from shared-memory
+//                   descriptors; tcgen05.commit frees the stage and, at the end, signals
+//                   the epilogue
+//   all four warps  epilogue: tcgen05.ld their 32 lanes of D into shared memory, then store
+//                   (bfloat16 or float, or silu(gate) * up), after adding the partial sums
+//                   of the other blocks when K is split
+//
+// With split K the blocks of a cluster (2, 4 or 8 along K) each keep a float partial
+// [Mpad x 128] in their own shared memory; after a cluster barrier block r of the cluster
+// adds the partials of all blocks, in rank order, over distributed shared memory for its
+// share of the rows and stores them.  The order is fixed, so results do not depend on timing.
+//
+// Every wait on an mbarrier is bounded: when it gives up the kernel records that in the
+// error record, skips its stores, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace {
+constexpr int TILE_ROWS = 128;   // rows of W per block (UMMA M)
+constexpr int KSTEP = 64;        // elements of K per TMA box: one 128-byte swizzle row
+constexpr int KSUB_MAX = 4;      // boxes per stage
+constexpr int TC_THREADS = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+#define DK_DEV_TIMEOUT 4
+
+__device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// false when the wait gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);         // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
+  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                         // 128-byte swizzle
+  return d;
+}
+// instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128
+__device__ __forceinline__ uint32_t instr_desc(int n) {
+  uint32_t d = 0;
+  d |= 1u << 4;                      // D is float
+  d |= 1u << 7;                      // A is bfloat16
+  d |= 1u << 10;                     // B is bfloat16
+  d |= (uint32_t)(n >> 3) << 17;     // N / 8
+  d |= (uint32_t)(TILE_ROWS >> 4) << 24;   // M / 16
+  return d;
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcArgs {
+  void* out;         // [M, ldc] bfloat16 or float
+  int* err;
+  int M, N, K, ldc;
+  int mpad;          // M rounded up to a multiple of 16: the N of the MMA
+  int stages;
+  int out_f32;
+  int swiglu;        // rows of the tile: 64 gate rows then the 64 up rows that belong to them
+  int n_up;          // first up row in W (= columns of the output) when swiglu
+  int tmem_cols;
+  int ksub;          // boxes of 64 elements of K per stage (4, or 2 when many rows leave less room)
+};
+
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                             const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the ring of stages starts on a 1024-byte boundary (the swizzle pattern repeats every 1024 bytes)
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int a_bytes = TILE_ROWS * KSTEP * 2;          // one box of W
+  const int b_bytes = a.mpad * KSTEP * 2;             // one box of x (a multiple of 2048)
+  const int KSUB = a.ksub;
+  const int stage_bytes = KSUB * (a_bytes + b_bytes);
+  __shared__ __align__(8) unsigned long long bars[2 * 16 + 1];   // full[s], empty[s], tmem_full
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int splits = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int tile = blockIdx.x;                       // 128 rows of W (64 + 64 with the SwiGLU epilogue)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rows_out = a.swiglu ? 64 : TILE_ROWS;    // output columns this tile makes
+  const int n0 = tile * rows_out;
+
+  const int k_steps_total = (a.K + KSTEP * KSUB - 1) / (KSTEP * KSUB);
+  const int per = (k_steps_total + splits - 1) / splits;
+  const int ks_begin = rank * per;
+  const int ks_end = min(k_steps_total, ks_begin + per);
+  const int n_steps = max(0, ks_end - ks_begin);
+
+  const uint32_t full0 = s2u(&bars[0]), empty0 = s2u(&bars[16]), tfull = s2u(&bars[32]);
+  if (tid == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(tfull, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {   // one warp allocates the tensor memory for the accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s2u(&tmem_base_slot)), "r"(a.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (tid == 0) {
+    // producer
+    for (int i = 0; i < n_steps; ++i) {
+      const int s = i % a.stages;
+      if (i >= a.stages && !mbar_wait(empty0 + 8 * s, ((i / a.stages) - 1) & 1)) {
+        failed = 1;
+        break;
+      }
+      const uint32_t dst0 = s2u(smem + (size_t)s * stage_bytes);
+      mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
+      for (int sub = 0; sub < KSUB; ++sub) {
+        const int kc = ((ks_begin + i) * KSUB + sub) * KSTEP;     // past K the boxes are filled with zeros
+        const uint32_t dst = dst0 + sub * a_bytes;
+        if (a.swiglu) {
+          tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);                           // 64 gate rows
+          tma_load_2d(dst + 64 * KSTEP * 2, &map_w, kc, a.n_up + n0, full0 + 8 * s);  // their 64 up rows
+        } else {
+          tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);
+        }
+        tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, 0, full0 + 8 * s);
+      }
+    }
+  } else if (tid == 32) {
+    // MMA issuer
+    const uint32_t idesc = instr_desc(a.mpad);
+    for (int i = 0; i < n_steps; ++i) {
+      const int s = i % a.stages;
+      if (!mbar_wait(full0 + 8 * s, (i / a.stages) & 1)) {
+        failed = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t sa = s2u(smem + (size_t)s * stage_bytes);
+      for (int sub = 0; sub < KSUB; ++sub) {
+        const uint64_t da = smem_desc(sa + sub * a_bytes), db = smem_desc(sa + KSUB * a_bytes + sub * b_bytes);
+#pragma unroll
+        for (int k = 0; k < KSTEP / 16; ++k)
+          umma(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || sub > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
+    }
+    umma_commit(tfull);                 // the accumulator is complete once everything issued is done
+  }
+  // epilogue: every warp reads its 32 lanes of D
+  __syncwarp();
+  bool good = true;
+  if (n_steps > 0) good = mbar_wait(tfull, 0);
+  tc_fence_after();
+  __syncthreads();
+  if (!good || failed) {
+    if (tid == 0) dk_report(a.err, DK_DEV_TIMEOUT, blockIdx.x, rank, n_steps);
+    good = false;
+  }
+  const int row = warp * 32 + lane;                  // row of D = row of the W tile
+  float* part = reinterpret_cast<float*>(smem);       // [mpad][128] floats, reuses the stages
+  // D -> shared memory, transposed so that a token's 128 outputs are contiguous
+  for (int c0 = 0; c0 < a.mpad; c0 += 16) {
+    float v[16];
+    if (good && n_steps > 0) {
+      tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) part[(size_t)(c0 + i) * TILE_ROWS + row] = v[i];
+  }
+  tc_fence_before();
+  if (splits > 1) cluster.sync(); else __syncthreads();
+
+  // block r of the cluster finishes rows [r * share, (r + 1) * share) of the tile
+  const int share = rows_out / splits;
+  const int r_begin = rank * share;
+  for (int idx = tid; idx < share * a.M; idx += TC_THREADS) {
+    const int m = idx / share, r = r_begin + idx % share;
+    float g = 0.f, u = 0.f;
+    for (int b = 0; b < splits; ++b) {
+      const float* src = splits > 1 ? cluster.map_shared_rank(part, b) : part;
+      g += src[(size_t)m * TILE_ROWS + r];
+      if (a.swiglu) u += src[(size_t)m * TILE_ROWS + 64 + r];
+    }
+    const int n = n0 + r;
+    if (good && n < (a.swiglu ? a.n_up : a.N)) {
+      const float y = a.swiglu ? g / (1.f + expf(-g)) * u : g;
+      if (a.out_f32) ((float*)a.out)[(size_t)m * a.ldc + n] = y;
+      else ((__nv_bfloat16*)a.out)[(size_t)m * a.ldc + n] = __float2bfloat16_rn(y);
+    }
+  }
+  if (splits > 1) cluster.sync(); else __syncthreads();   // nobody leaves while its memory is still read
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) return nullptr;
+  fn = (EncodeFn)p;
+  return fn;
+}
+
+// 2-D bfloat16 tensor [rows, K] with leading size ld: boxes of [box_rows x 64], 128-byte swizzle
+bool make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+extern "C" int dk_gemm_tc_supported(int M, int N, int K, int swiglu) {
+  if (M < 1 || M > 128 || K < 64 || (K % 8) != 0) return 0;
+  if (swiglu) {
+    if ((N % 2) != 0 || ((N / 2) % 64) != 0) return 0;
+  } else if ((N % 8) != 0) {
+    return 0;
+  }
+  return 1;
+}
+
+// splits: blocks that share K as one cluster (1, 2, 4 or 8).  out_dtype DK_BF16 or DK_F32.
+extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int lda, int ldw, int ldc,
+                          int out_dtype, int swiglu, int splits, int* err, cudaStream_t stream) {
+  DK_REQUIRE(dk_gemm_tc_supported(M, N, K, swiglu), "gemm_tc: sizes not taken: M=%d N=%d K=%d swiglu=%d", M, N, K, swiglu);
+  DK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: splits must be 1, 2, 4 or 8, got %d", splits);
+  DK_REQUIRE((lda % 8) == 0 && (ldw % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0,
+             "gemm_tc: operands must start on 16-byte boundaries with leading sizes that are multiples of 8");
+  DK_REQUIRE(out_dtype == DK_BF16 || out_dtype == DK_F32, "gemm_tc: unknown output dtype %d", out_dtype);
+  TcArgs a;
+  a.out = out;
+  a.err = err;
+  a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  a.mpad = (M + 15) / 16 * 16;
+  a.out_f32 = out_dtype == DK_F32;
+  a.swiglu = swiglu;
+  a.n_up = swiglu ? N / 2 : 0;
+  a.tmem_cols = a.mpad <= 32 ? 32 : (a.mpad <= 64 ? 64 : 128);
+  const int a_bytes = TILE_ROWS * KSTEP * 2;
+  const int b_bytes = a.mpad * KSTEP * 2;
+  a.ksub = a.mpad <= 64 ? KSUB_MAX : 2;
+  const int stage_bytes = a.ksub * (a_bytes + b_bytes);
+  const int part_bytes = a.mpad * TILE_ROWS * 4;
+  int stages = (224 * 1024 - 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  DK_REQUIRE(stages >= 2, "gemm_tc: M=%d leaves no room for two stages", M);
+  a.stages = stages;
+  size_t smem = (size_t)stages * stage_bytes;
+  if (smem < (size_t)part_bytes) smem = part_bytes;
+  smem += 1024;
+  CUtensorMap map_w, map_x;
+  DK_REQUIRE(make_map(&map_w, W, N, K, ldw, swiglu ? 64 : TILE_ROWS), "gemm_tc: cannot encode the tensor map of W");
+  DK_REQUIRE(make_map(&map_x, x, M, K, lda, a.mpad), "gemm_tc: cannot encode the tensor map of x");
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      dk_set_error("gemm_tc: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = smem;
+  }
+  const int rows_out = swiglu ? 64 : TILE_ROWS;
+  const int n_out = swiglu ? N / 2 : N;
+  const int tiles = (n_out + rows_out - 1) / rows_out;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles, splits, 1);
+  cfg.blockDim = dim3(TC_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = splits;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_w, map_x, a);
+  if (e != cudaSuccess) {
+    dk_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
+    return DK_ERR_LAUNCH;
+  }
+  return dk_check_launch("gemm_tc");
+}

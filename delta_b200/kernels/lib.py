@@ -54,6 +54,8 @@ _SIGNATURES = {
     "dk_attention_prefill_supported": [I, I, I, I, I],
     "dk_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_gemm_small_m_supported": [I, I, I, I],
+    "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+    "dk_gemm_tc_supported": [I, I, I, I],
 }
 
 

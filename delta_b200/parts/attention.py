@@ -115,7 +115,10 @@ class GQAAttention(Mixer):
                              ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), self.keep_last, cache.page_size,
                              self.bias, self.ratio)
             if ctx.capture is not None:
-                ctx.capture.setdefault("page_scores", []).append((self.prefix, scores.clone()))
-                ctx.capture.setdefault("selected", []).append(
-                    (self.prefix, ctx.state(SELECTED_PAGES).clone(), ctx.state(SELECTED_COUNT).clone()))
+                # for tests: what this planner chose, per (part, request slot, position)
+                pages, counts = ctx.state(SELECTED_PAGES).cpu(), ctx.state(SELECTED_COUNT).cpu()
+                planned = ctx.capture.setdefault("planned", {})
+                for r in ctx.host["rows"]:
+                    if r.selective and int(counts[r.slot]) >= 0:
+                        planned[(self.prefix, r.slot, r.start_pos)] = pages[r.slot, :int(counts[r.slot])].tolist()
         return linear.linear(ctx, out, self.w_o)

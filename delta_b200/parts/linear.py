@@ -2,29 +2,125 @@
 
 32-bit activations go through the plain FMA kernel (true 32 bit: no
 reduced-precision matrix mode, no split over K).  bfloat16 activations go
-through the tensor cores: the library product that the reference uses for its
-``nn.Linear`` layers (DELTA/Engine/DELTA/model.py:369-370, 498-500), or the
-hand-written kernels where they are faster.
+through the tensor cores.  For large batches (prompt portions) that is the
+library product the reference uses for its ``nn.Linear`` layers
+(DELTA/Engine/DELTA/model.py:369-370, 498-500).  For the few rows of a decode
+step the product is a stream over the weights and three kernels compete: the
+tcgen05/TMA kernel (with 1, 2, 4 or 8 blocks sharing K as a cluster), the
+warp-level MMA kernel that loads weights straight into fragments, and the
+library.  Which one is fastest depends on the shape, so each (rows bucket, N, K,
+epilogue) is measured once on the real weights, with the L2 flushed between runs,
+and the winner is kept.
 """
 from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
 
 import torch
 
 from ..kernels import ops
 
+SMALL_M = 128          # up to this many rows a product counts as weight streaming and is tuned
+_BUCKETS = (8, 16, 32, 64, 128)
+_choice: Dict[tuple, str] = {}
+_flush: Optional[torch.Tensor] = None
+TUNE = os.environ.get("DELTA_B200_NO_TUNE") != "1"   # off: the first candidate of a shape is taken unmeasured
 
-SMALL_M = 64   # up to this many rows the product streams the weights once (decode steps)
+
+def _bucket(m: int) -> int:
+    for b in _BUCKETS:
+        if m <= b:
+            return b
+    return 0
+
+
+def _candidates(m: int, n: int, k: int, swiglu: bool, out_dtype) -> List[str]:
+    c = []
+    if m <= 64 and ops.gemm_small_m_supported(m, n, k, swiglu):
+        c.append("small")
+    if ops.gemm_tc_supported(m, n, k, swiglu):
+        for s in (1, 2, 4, 8):
+            if s == 1 or k // (256 * s) >= 2:
+                c.append(f"tc{s}")
+    if out_dtype == torch.bfloat16:
+        c.append("lib")
+    return c
+
+
+def _run(kind: str, x, w, out, swiglu: bool, err=None):
+    if kind == "small":
+        return ops.gemm_small_m(x, w, out, swiglu=swiglu)
+    if kind.startswith("tc"):
+        return ops.gemm_tc(x, w, out, swiglu=swiglu, splits=int(kind[2:]), err=err)
+    ops.count_launch()
+    if swiglu:
+        gu = torch.mm(x, w.t())
+        return ops.silu_mul(gu, out)
+    return torch.mm(x, w.t(), out=out)
+
+
+def _tune(m: int, x, w, swiglu: bool, out_dtype, err) -> str:
+    """Times every candidate on these weights with ``m`` rows and returns the fastest."""
+    global _flush
+    n, k = w.shape
+    cands = _candidates(m, n, k, swiglu, out_dtype)
+    if not cands:
+        return "none"
+    if len(cands) == 1 or not TUNE or torch.cuda.is_current_stream_capturing():
+        return cands[0]
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device=x.device)   # larger than the L2
+    xs = torch.randn((m, k), device=x.device, dtype=torch.float32).to(x.dtype)
+    out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+    best, best_t = cands[0], float("inf")
+    for kind in cands:
+        try:
+            _run(kind, xs, w, out, swiglu, err)
+            times = []
+            for _ in range(3):
+                _flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                _run(kind, xs, w, out, swiglu, err)
+                e1.record()
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1))
+            t = min(times)
+        except ops.KernelError:
+            continue
+        if t < best_t:
+            best, best_t = kind, t
+    return best
+
+
+def choose(m: int, w: torch.Tensor, x: torch.Tensor, swiglu: bool, out_dtype, err=None) -> str:
+    key = (_bucket(m), w.shape[0], w.shape[1], swiglu, out_dtype)
+    kind = _choice.get(key)
+    if kind is None:
+        kind = _tune(key[0], x, w, swiglu, out_dtype, err)
+        if not torch.cuda.is_current_stream_capturing():
+            _choice[key] = kind
+    return kind
+
+
+def choices() -> Dict[tuple, str]:
+    """What the measurements chose so far: (rows bucket, N, K, swiglu, out dtype) -> kernel."""
+    return dict(_choice)
 
 
 def swiglu_linear(ctx, x: torch.Tensor, w_gate_up: torch.Tensor):
-    """silu(x gate^T) * (x up^T) in one kernel when the batch is small enough; else None."""
-    T, N, K = x.shape[0], w_gate_up.shape[0], x.shape[1]
+    """silu(x gate^T) * (x up^T) with the gate fused into the product's epilogue when the batch
+    is small enough for the streaming kernels; else None."""
+    T = x.shape[0]
     if x.dtype != torch.bfloat16 or ctx.plain_products or not (0 < T <= SMALL_M):
         return None
-    if not ops.gemm_small_m_supported(T, N, K, swiglu=True):
+    kind = choose(T, w_gate_up, x, True, x.dtype, ctx.err)
+    if kind == "none":
         return None
-    out = torch.empty((T, N // 2), dtype=x.dtype, device=x.device)
-    return ops.gemm_small_m(x, w_gate_up, out, swiglu=True)
+    out = torch.empty((T, w_gate_up.shape[0] // 2), dtype=x.dtype, device=x.device)
+    _run(kind, x, w_gate_up, out, True, ctx.err)
+    return out
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
@@ -36,9 +132,12 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tenso
         if T:
             ops.gemm_nt_plain(x, w, out)
         return out
-    if 0 < T <= SMALL_M and ops.gemm_small_m_supported(T, N, x.shape[1]):
-        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
-        return ops.gemm_small_m(x, w, out)
+    if 0 < T <= SMALL_M:
+        kind = choose(T, w, x, False, out_dtype, ctx.err)
+        if kind != "none":
+            out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+            _run(kind, x, w, out, False, ctx.err)
+            return out
     if out_dtype == x.dtype:
         ops.count_launch()
         return torch.mm(x, w.t())

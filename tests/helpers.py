@@ -111,7 +111,7 @@ def mixed(lengths, prompt_lens, seed=0, max_live=4, portion_sizes=(5, 2, 11, 3, 
 
 # ---- running a schedule through the engine's step function -----------------------
 
-def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, selective=False):
+def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, selective=False, planned=None):
     """Feeds the schedule through ``runner`` (a ModelRunner) and returns
     {(request, position): logits row (CPU float32)}.  Logits are asked for at every
     token.  With ``selective`` the single tokens at or after a request's prompt
@@ -119,6 +119,8 @@ def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, select
     from delta_b200.engine.step import RowInput
     slots = {}
     out = {}
+    if planned is not None:
+        runner.capture = {}
     for k, step in enumerate(steps):
         rows, keys = [], []
         for (i, start, count) in step:
@@ -129,6 +131,11 @@ def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, select
             keys.extend((i, start + j) for j in range(count))
         logits = runner.run_rows(rows).float().cpu()
         assert logits.shape[0] == len(keys)
+        if planned is not None:
+            # what the planner layers chose in this step: {(request, layer, position): pages}
+            who = {s: i for i, s in slots.items()}
+            for (prefix, slot, pos), pages in runner.capture.pop("planned", {}).items():
+                planned[(who[slot], int(prefix.split(".")[2]), pos)] = pages
         for key, row in zip(keys, logits):
             assert key not in out, f"position {key} was fed twice"
             out[key] = row
@@ -138,6 +145,8 @@ def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, select
     for i in list(slots):
         runner.cache.release_slot(slots.pop(i))
     runner.cache.check()
+    if planned is not None:
+        runner.capture = None
     return out
 
 

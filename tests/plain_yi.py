@@ -292,7 +292,7 @@ class PlainYi:
         m = swiglu(f, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"], w[pre + "mlp.down_proj.weight"], self.rnd)
         return self._r(h + m), (k, v), s
 
-    def forward(self, tokens, selective: Selective | None = None) -> torch.Tensor:
+    def forward(self, tokens, selective: Selective | None = None, forced: dict | None = None) -> torch.Tensor:
         """Logits [T, V] of one whole sequence (DELTA/Engine/DELTA/model.py:198-206,
         without the argmax of line 323).  With ``selective`` the positions from
         ``prompt_len`` on are decode positions: in subset layers they see only the
@@ -312,6 +312,7 @@ class PlainYi:
                     chosen[p] = recent_pages(n, selective.k)
         caches = {}
         self.last_selection = {}
+        self.last_planned = {}     # (planner layer, position) -> pages it chose
         for (i, cache_id, writes) in c.plan:
             # a layer with a window reads a bounded number of keys already and takes no page selection
             role = selective.role(i, c.layers) if (selective and c.windows[i] is None) else "full"
@@ -331,8 +332,14 @@ class PlainYi:
                 for p in range(selective.prompt_len, T):
                     n = p // ps + 1
                     if selection_active(n, selective.k, selective.ratio):
+                        if forced is not None and (i, p) in forced:
+                            # attend to the pages somebody else chose (a comparison in reduced precision,
+                            # where two nearly equal page scores may come out in the other order)
+                            chosen[p] = list(forced[(i, p)])
+                            continue
                         sc = page_scores(s[:, p, :p + 1], p + 1, ps)
                         chosen[p] = select_pages(sc, n, selective.k, selective.L)
+                        self.last_planned[(i, p)] = list(chosen[p])
         x = self._r(rms_norm(x, w["model.norm.weight"], c.eps, self.rnd))
         return (x @ w["lm_head.weight"].T).to(torch.float32)
 

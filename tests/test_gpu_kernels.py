@@ -12,6 +12,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(1234)
+
+
 def ops():
     from delta_b200.kernels import ops as o
     return o
@@ -161,6 +166,49 @@ def test_gemm_small_m(M, N, K):
     act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
     o.gemm_small_m(x, w, act, swiglu=True)
     want = torch.nn.functional.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+    assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 100, 128])
+@pytest.mark.parametrize("N, K, splits", [(128, 64, 1), (1000, 344, 1), (4096, 4096, 4), (1408, 11008, 8), (2048, 520, 2)])
+def test_gemm_tc(M, N, K, splits):
+    """The tcgen05/TMA product: one block per 128 weight rows, K shared by a cluster of blocks
+    whose partial sums are added over distributed shared memory; sizes that end inside a tile,
+    inside a 64-element box and inside a stage of several boxes."""
+    o = ops()
+    torch.manual_seed(M * 7 + splits)
+    err = o.new_error_record(DEV)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x, w, out, splits=splits, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2)
+    out32 = torch.full((M, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_tc(x, w, out32, splits=splits, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(out32, ref, atol=1e-3, rtol=1e-4)
+    # the same result whatever the split: float sums of K terms below 0.1 in another order differ
+    # by at most about K * 2^-24 * 0.1, which is 7e-5 for the longest K here
+    other = torch.empty_like(out32)
+    o.gemm_tc(x, w, other, splits=1, err=err)
+    assert torch.allclose(other, out32, atol=5e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("M", [3, 64])
+@pytest.mark.parametrize("I, K, splits", [(64, 128, 1), (704, 344, 1), (11008, 4096, 2)])
+def test_gemm_tc_swiglu(M, I, K, splits):
+    o = ops()
+    torch.manual_seed(M + I)
+    err = o.new_error_record(DEV)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    want = torch.nn.functional.silu(ref[:, :I]) * ref[:, I:]
+    act = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x, w, act, swiglu=True, splits=splits, err=err)
+    o.raise_if_error(err)
     assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
 
 

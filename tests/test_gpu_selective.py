@@ -20,9 +20,23 @@ CASES = [
 ]
 
 
+def plain_logits(plain, toks, prompt_lens, sel, ps, forced=None):
+    refs, planned = [], {}
+    for i, (t, pl) in enumerate(zip(toks, prompt_lens)):
+        f = None if forced is None else {(l, p): pg for (r, l, p), pg in forced.items() if r == i}
+        refs.append(plain.forward(t, Selective(list(sel.full_cache_layers), sel.subset_cache_size, sel.L,
+                                               sel.compression_ratio, ps, pl), forced=f))
+        planned.update({(i, l, p): pg for (l, p), pg in plain.last_planned.items()})
+    return refs, planned
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which, full, k, L, ratio", CASES)
 def test_selective_cache(model_folders, which, full, k, L, ratio, dtype):
+    """In 32 bit the engine chooses the pages the plain implementation chooses, and the logits
+    agree.  In bfloat16 two nearly equal page scores may come out in the other order, so there
+    the plain implementation attends to the pages the engine chose (and the two choices must
+    still agree almost everywhere)."""
     from delta_b200.config import EngineConfig, SelectiveCacheConfig
     from delta_b200.engine.step import ModelRunner
     folder = model_folders[which]
@@ -32,30 +46,39 @@ def test_selective_cache(model_folders, which, full, k, L, ratio, dtype):
     prompt_lens = [9, 20, 35, 40]
     plain = PlainYi(folder, rounding="bfloat16" if dtype == "bfloat16" else None)
     toks = [helpers.random_tokens(n, plain.cfg.vocab, 40 + i) for i, n in enumerate(lengths)]
-    refs, chosen = [], []
-    for t, pl in zip(toks, prompt_lens):
-        refs.append(plain.forward(t, Selective(list(full), k, L, ratio, ps, pl)))
-        chosen.append(dict(plain.last_selection))
-    assert any(chosen), "the case never selected anything"
+    refs, want = plain_logits(plain, toks, prompt_lens, sel, ps)
+    assert want, "the case never selected anything"
 
     def runner(num_pages):
         cfg = EngineConfig(max_batch=4, max_seq_len=256, page_size=ps, num_pages=num_pages, dtype=dtype, selective=sel)
         return ModelRunner(folder, engine_config=cfg)
+
+    def check(res, got, what):
+        assert set(got) == set(want), f"{what}: the engine planned at other (request, layer, position) places"
+        if dtype == "float32":
+            assert got == want, f"{what}: the engine chose other pages"
+            compare(res, refs, lengths, dtype, what)
+        else:
+            same = sum(got[key] == want[key] for key in want)
+            assert same >= 0.9 * len(want), f"{what}: only {same} of {len(want)} choices agree"
+            forced_refs, _ = plain_logits(plain, toks, prompt_lens, sel, ps, forced=got)
+            compare(res, forced_refs, lengths, dtype, what)
 
     # each request alone: the prompt in one step, then token by token
     steps = []
     for i, (n, pl) in enumerate(zip(lengths, prompt_lens)):
         steps.append([(i, 0, pl)])
         steps.extend([[(i, p, 1)] for p in range(pl, n)])
-    r = runner(4 * (256 // ps))
-    res = helpers.run_schedule(r, toks, steps, prompt_lens=prompt_lens, selective=True)
-    compare(res, refs, lengths, dtype, "alone")
+    got = {}
+    res = helpers.run_schedule(runner(4 * (256 // ps)), toks, steps, prompt_lens=prompt_lens, selective=True, planned=got)
+    check(res, got, "alone")
 
     # prompts in portions, decode tokens of several requests in one step, few pages
     sched, ends = helpers.mixed(lengths, prompt_lens, seed=5)
-    r2 = runner(helpers.peak_pages(sched, ends, ps))
-    res = helpers.run_schedule(r2, toks, sched, ends, prompt_lens=prompt_lens, selective=True)
-    compare(res, refs, lengths, dtype, "mixed")
+    got = {}
+    res = helpers.run_schedule(runner(helpers.peak_pages(sched, ends, ps)), toks, sched, ends, prompt_lens=prompt_lens,
+                               selective=True, planned=got)
+    check(res, got, "mixed")
 
 
 def test_chosen_pages_equal_the_plain_ones(model_folders):
