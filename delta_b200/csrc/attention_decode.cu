@@ -404,3 +404,57 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
              "attention_decode: chosen pages are given without their counts, row flags or slots");
   return p.hd == 64 ? launch<64>(p, stream) : launch<128>(p, stream);
 }
+
+// --------------------------------------------------------------------------------------
+// The same launch with its scratch inside the library, for callers that cannot allocate
+// (see no_alloc.h).  In host code the name of a __device__ array is only a handle for the
+// runtime, not an address a kernel can use, so the address is asked for once per device.
+#include "no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_scratch[DK_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_addr[MAX_DEVICES] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the built-in scratch on the current device, or nullptr with the error set.
+float* static_scratch_address() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    dk_set_error("attention_decode_static: cannot tell the current device (%s)", cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      dk_set_error("attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  return g_static_scratch_addr[dev];
+}
+}  // namespace
+
+extern "C" int dk_attention_decode_static(const DkAttnParams* pp, cudaStream_t stream) {
+  DK_REQUIRE(pp != nullptr, "attention_decode_static: no parameters");
+  DkAttnParams p = *pp;
+  p.scratch = nullptr;
+  if (p.rows == 0) return 0;
+  const long long need = dk_attention_decode_scratch_floats(p.rows, p.H, p.hd, p.splits);
+  DK_REQUIRE(need <= (long long)DK_STATIC_SCRATCH_FLOATS,
+             "attention_decode_static: %d rows x %d heads x %d splits x head size %d need %lld floats of scratch, the "
+             "built-in buffer holds %d; use fewer splits or rows, or dk_attention_decode with a buffer of your own",
+             p.rows, p.H, p.splits, p.hd, need, (int)DK_STATIC_SCRATCH_FLOATS);
+  if (p.splits > 1) {
+    float* addr = static_scratch_address();
+    if (addr == nullptr) return DK_ERR_LAUNCH;
+    p.scratch = addr;
+  }
+  return dk_attention_decode(&p, stream);
+}
