@@ -120,31 +120,50 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     }
   }
 
-  auto load_tile = [&](int tile, int stage) {
-    unsigned char* kdst = kv_smem + (size_t)stage * 2 * TILE_BYTES;
-    unsigned char* vdst = kdst + TILE_BYTES;
+  // What does not change from tile to tile is worked out once: which key of a tile each of this
+  // thread's 16-byte chunks belongs to, where it lands in shared memory, where it sits in a page.
+  constexpr int LOADS = TILE * CHUNKS / NTHREADS;
+  const int part = tid % CHUNKS;
+  int ld_tok[LOADS], ld_pg[LOADS], ld_src[LOADS], ld_dst[LOADS];
 #pragma unroll
-    for (int i = 0; i < TILE * CHUNKS / NTHREADS; ++i) {
-      const int c = tid + i * NTHREADS;
-      const int tok = c / CHUNKS, part = c % CHUNKS;
-      const int el = tile * pages_per_tile + tok / ps, off = tok % ps;
+  for (int i = 0; i < LOADS; ++i) {
+    const int tok = (tid + i * NTHREADS) / CHUNKS;
+    ld_tok[i] = tok;
+    ld_pg[i] = tok / ps;
+    ld_src[i] = (tok % ps) * HD + part * 8;                       // elements inside the (page, K, head) block
+    ld_dst[i] = tok * ROW_BYTES + ((part ^ (tok & 7)) * 16);      // bytes inside a K or V tile
+  }
+  const size_t page_stride = (size_t)2 * p.KV * ps * HD;           // elements from one page to the next
+  const size_t v_offset = (size_t)p.KV * ps * HD;                  // from a page's K to its V
+  const __nv_bfloat16* kv_head = kv + (size_t)kvh * ps * HD;
+
+  // returns whether every chunk this thread asked for belongs to a key the query may see
+  auto load_tile = [&](int tile, int stage) -> bool {
+    const uint32_t kdst = smem_u32(kv_smem + (size_t)stage * 2 * TILE_BYTES);
+    const uint32_t vdst = kdst + TILE_BYTES;
+    const int el0 = tile * pages_per_tile;
+    bool all_valid = true;
+#pragma unroll
+    for (int i = 0; i < LOADS; ++i) {
+      const int el = el0 + ld_pg[i];
       bool valid = false;
-      size_t koff = 0;
       int key = -1;
+      const __nv_bfloat16* src = kv_head;
       if (e_begin + el < e_end) {
         const int page = s_page[el];
-        const int k = s_lp[el] * ps + off;
+        const int k = s_lp[el] * ps + (ld_tok[i] % ps);
         if (page >= 0 && k >= ri.lo && k <= ri.pos) {
           valid = true;
           key = k;
-          koff = ((((size_t)page * 2 + 0) * p.KV + kvh) * ps + off) * HD + part * 8;
+          src = kv_head + (size_t)page * page_stride + ld_src[i];
         }
       }
-      const int sw = (part ^ (tok & 7)) * 16;
-      cp_async_16(smem_u32(kdst + tok * ROW_BYTES + sw), kv + koff, valid);
-      cp_async_16(smem_u32(vdst + tok * ROW_BYTES + sw), kv + koff + (size_t)p.KV * ps * HD, valid);
-      if (part == 0) s_key[stage * TILE + tok] = key;
+      all_valid &= valid;
+      cp_async_16(kdst + ld_dst[i], src, valid);
+      cp_async_16(vdst + ld_dst[i], src + v_offset, valid);
+      if (part == 0) s_key[stage * TILE + ld_tok[i]] = key;
     }
+    return all_valid;
   };
 
   float o[NT][4];
@@ -155,19 +174,33 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   const float sc_log2 = p.scale * 1.4426950408889634f;
 
 #pragma unroll
+  // full[s]: every key of the tile in stage s is one the query may see, so its scores need no
+  // masking.  Each thread knows it for its own chunks; the barriers below collect the votes.
+  unsigned full = 0;   // bit s: stage s
+#pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(s, s);
+    bool mine = true;
+    if (s < n_tiles) mine = load_tile(s, s);
     cp_async_commit();
+    if (__syncthreads_and(mine)) full |= 1u << s;
   }
+  bool issued_ok = true;
   for (int tile = 0; tile < n_tiles; ++tile) {
     cp_async_wait<STAGES - 2>();
-    __syncthreads();
     {
+      // the barrier also tells whether the tile issued in the iteration before is wholly visible
+      const bool prev = __syncthreads_and(issued_ok) != 0;
+      if (tile > 0) {
+        const unsigned bit = 1u << ((tile - 1 + STAGES - 1) % STAGES);
+        full = prev ? (full | bit) : (full & ~bit);
+      }
       const int nxt = tile + STAGES - 1;
-      if (nxt < n_tiles) load_tile(nxt, nxt % STAGES);
+      issued_ok = true;
+      if (nxt < n_tiles) issued_ok = load_tile(nxt, nxt % STAGES);
       cp_async_commit();
     }
     const int stage = tile % STAGES;
+    const bool no_mask = ((full >> stage) & 1u) && !ri.dumping;
     const uint32_t kbase = smem_u32(kv_smem + (size_t)stage * 2 * TILE_BYTES);
     const uint32_t vbase = kbase + TILE_BYTES;
     const int* keys = s_key + stage * TILE + warp * 16;
@@ -190,6 +223,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     }
     // mask, dump, online softmax (values in log2 units)
     float tmax[2] = {-INFINITY, -INFINITY};
+    if (no_mask) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          s[j][c] *= sc_log2;
+          tmax[c >> 1] = fmaxf(tmax[c >> 1], s[j][c]);
+        }
+    } else
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
 #pragma unroll
@@ -241,13 +283,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
       pa[2] = pack_bf16(pv[1][0], pv[1][1]);
       pa[3] = pack_bf16(pv[1][2], pv[1][3]);
     }
-    // O = O * corr + P V
+    // O = O * corr + P V; once the maxima have settled corr is 1 and the scaling is skipped
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      o[n][0] *= corr[0];
-      o[n][1] *= corr[0];
-      o[n][2] *= corr[1];
-      o[n][3] *= corr[1];
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+      }
     }
     {
       const int tok = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
