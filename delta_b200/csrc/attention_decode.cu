@@ -35,10 +35,14 @@ struct RowInfo {
 
 __device__ __forceinline__ RowInfo row_info(const DkAttnParams& p, int row) {
   RowInfo r;
-  r.t = p.row_q_start[row] + p.row_q_len[row] - 1;
-  r.pos = p.tok_pos[r.t];
+  // independent loads first: the position follows from the row's start and length, so that
+  // nothing here waits for another load except the count of chosen pages
+  const int q_start = p.row_q_start[row], q_len = p.row_q_len[row];
+  const int pos_start = p.row_pos_start ? p.row_pos_start[row] : -1;
   r.slot = p.row_slot ? p.row_slot[row] : row;
   const int flags = p.row_flags ? p.row_flags[row] : 0;
+  r.t = q_start + q_len - 1;
+  r.pos = pos_start >= 0 ? pos_start + q_len - 1 : p.tok_pos[r.t];
   int n_sel = -1;
   if (p.sel_pages != nullptr && (flags & 1)) n_sel = p.sel_count[r.slot];
   r.subset = n_sel >= 0;
@@ -58,8 +62,25 @@ __device__ __forceinline__ size_t part_ml_index(const DkAttnParams& p, int row, 
   return (size_t)p.rows * p.H * p.splits * p.hd + (((size_t)row * p.H + h) * p.splits + split) * 2;
 }
 
-template <int HD>
+// LOW: at most 8 query heads per key-value head.  Rows 8..15 of the MMA tile are then empty;
+// their accumulators are two dummy registers that stay zero, and the softmax and the output
+// keep one row per thread instead of two, which halves that work and frees registers.
+template <bool LOW>
+__device__ __forceinline__ void mma_rows(float* c, float (&zd)[2], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (LOW) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(zd[0]), "+f"(zd[1])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+template <int HD, bool LOW>
 __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkAttnParams p) {
+  constexpr int R = LOW ? 1 : 2;              // rows of the tile a thread keeps (g, and g + 8)
   constexpr int CHUNKS = HD / 8;              // 16-byte chunks per key row
   constexpr int ROW_BYTES = HD * 2;
   constexpr int TILE_BYTES = TILE * ROW_BYTES;  // one of K or V
@@ -114,12 +135,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     for (int kb = 0; kb < KB; ++kb) {
       const int c = kb * 16 + 2 * tq;
       qa[kb][0] = g < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + c) : 0u;
-      qa[kb][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c) : 0u;
+      qa[kb][1] = (!LOW && g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c) : 0u;
       qa[kb][2] = g < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + c + 8) : 0u;
-      qa[kb][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c + 8) : 0u;
+      qa[kb][3] = (!LOW && g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c + 8) : 0u;
     }
   }
-
   // What does not change from tile to tile is worked out once: which key of a tile each of this
   // thread's 16-byte chunks belongs to, where it lands in shared memory, where it sits in a page.
   constexpr int LOADS = TILE * CHUNKS / NTHREADS;
@@ -166,11 +186,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     return all_valid;
   };
 
-  float o[NT][4];
+  float o[NT][2 * R];
 #pragma unroll
-  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};  // rows g and g + 8, in units of log2
-  float l_run[2] = {0.f, 0.f};              // this thread's part of the row sums
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int c = 0; c < 2 * R; ++c) o[n][c] = 0.f;
+  float zd[2] = {0.f, 0.f};                 // accumulators of the empty rows (LOW)
+  float m_run[R], l_run[R];                 // rows g (and g + 8): running maximum in log2 units, this thread's part of the row sum
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.f;
+  }
   const float sc_log2 = p.scale * 1.4426950408889634f;
 
 #pragma unroll
@@ -206,9 +233,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     const int* keys = s_key + stage * TILE + warp * 16;
 
     // S = Q K^T for this warp's 16 keys (two n-tiles of 8)
-    float s[2][4];
+    float s[2][2 * R];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int c = 0; c < 2 * R; ++c) s[j][c] = 0.f;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int tok = warp * 16 + j * 8 + (lane & 7);
@@ -217,81 +246,72 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
         const int chunk = 2 * kb + (lane >> 3);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3, kbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
-        mma_bf16(s[j], qa[kb], b0, b1);
-        mma_bf16(s[j], qa[kb + 1], b2, b3);
+        mma_rows<LOW>(s[j], zd, qa[kb], b0, b1);
+        mma_rows<LOW>(s[j], zd, qa[kb + 1], b2, b3);
       }
     }
     // mask, dump, online softmax (values in log2 units)
-    float tmax[2] = {-INFINITY, -INFINITY};
+    float tmax[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) tmax[r] = -INFINITY;
     if (no_mask) {
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2 * R; ++c) {
           s[j][c] *= sc_log2;
           tmax[c >> 1] = fmaxf(tmax[c >> 1], s[j][c]);
         }
-    } else
+    } else {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < 2; ++j) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int key = keys[j * 8 + 2 * tq + c];
-        if (key < 0) {
-          s[j][c] = -INFINITY;
-          s[j][2 + c] = -INFINITY;
-        } else {
-          if (ri.dumping && key < p.dump_stride) {
-            if (g < G) p.dump[((size_t)row * p.H + kvh * G + g) * p.dump_stride + key] = s[j][c] * p.scale;
-            if (g + 8 < G) p.dump[((size_t)row * p.H + kvh * G + g + 8) * p.dump_stride + key] = s[j][2 + c] * p.scale;
+        for (int c = 0; c < 2; ++c) {
+          const int key = keys[j * 8 + 2 * tq + c];
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            float v = s[j][2 * r + c];
+            if (key < 0) {
+              v = -INFINITY;
+            } else {
+              if (ri.dumping && key < p.dump_stride && g + 8 * r < G)
+                p.dump[((size_t)row * p.H + kvh * G + g + 8 * r) * p.dump_stride + key] = v * p.scale;
+              v *= sc_log2;
+            }
+            s[j][2 * r + c] = v;
+            tmax[r] = fmaxf(tmax[r], v);
           }
-          s[j][c] *= sc_log2;
-          s[j][2 + c] *= sc_log2;
         }
-        tmax[0] = fmaxf(tmax[0], s[j][c]);
-        tmax[1] = fmaxf(tmax[1], s[j][2 + c]);
       }
     }
+    float corr[R], m_use[R];
+    bool moved = false;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < R; ++r) {
       tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
       tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-    }
-    float corr[2], m_use[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
       const float m_new = fmaxf(m_run[r], tmax[r]);
       m_use[r] = m_new == -INFINITY ? 0.f : m_new;   // a warp whose 16 keys are all masked
       corr[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] - m_use[r]);
+      moved |= corr[r] != 1.f;
       m_run[r] = m_new;
       l_run[r] *= corr[r];
     }
-    uint32_t pa[4];
-    {
-      float pv[2][4];
+    uint32_t pa[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        pv[j][0] = exp2f(s[j][0] - m_use[0]);
-        pv[j][1] = exp2f(s[j][1] - m_use[0]);
-        pv[j][2] = exp2f(s[j][2] - m_use[1]);
-        pv[j][3] = exp2f(s[j][3] - m_use[1]);
-        l_run[0] += pv[j][0] + pv[j][1];
-        l_run[1] += pv[j][2] + pv[j][3];
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float p0 = exp2f(s[j][2 * r] - m_use[r]), p1 = exp2f(s[j][2 * r + 1] - m_use[r]);
+        l_run[r] += p0 + p1;
+        pa[2 * j + r] = pack_bf16(p0, p1);
       }
-      pa[0] = pack_bf16(pv[0][0], pv[0][1]);
-      pa[1] = pack_bf16(pv[0][2], pv[0][3]);
-      pa[2] = pack_bf16(pv[1][0], pv[1][1]);
-      pa[3] = pack_bf16(pv[1][2], pv[1][3]);
-    }
     // O = O * corr + P V; once the maxima have settled corr is 1 and the scaling is skipped
-    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+    if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        o[n][0] *= corr[0];
-        o[n][1] *= corr[0];
-        o[n][2] *= corr[1];
-        o[n][3] *= corr[1];
-      }
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 2 * R; ++c) o[n][c] *= corr[c >> 1];
     }
     {
       const int tok = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -300,8 +320,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
         const int chunk = n + (lane >> 4);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
-        mma_bf16(o[n], pa, b0, b1);
-        mma_bf16(o[n + 1], pa, b2, b3);
+        mma_rows<LOW>(o[n], zd, pa, b0, b1);
+        mma_rows<LOW>(o[n + 1], zd, pa, b2, b3);
       }
     }
   }
@@ -310,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
 
   // merge the four warps through shared memory (the tiles are no longer needed)
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < R; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
@@ -320,16 +340,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
     float* base = w_o + ((size_t)warp * 16) * HD + n * 8 + 2 * tq;
-    base[(size_t)g * HD] = o[n][0];
-    base[(size_t)g * HD + 1] = o[n][1];
-    base[(size_t)(g + 8) * HD] = o[n][2];
-    base[(size_t)(g + 8) * HD + 1] = o[n][3];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      base[(size_t)(g + 8 * r) * HD] = o[n][2 * r];
+      base[(size_t)(g + 8 * r) * HD + 1] = o[n][2 * r + 1];
+    }
   }
   if (tq == 0) {
-    w_m[warp * 16 + g] = m_run[0];
-    w_m[warp * 16 + g + 8] = m_run[1];
-    w_l[warp * 16 + g] = l_run[0];
-    w_l[warp * 16 + g + 8] = l_run[1];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      w_m[warp * 16 + g + 8 * r] = m_run[r];
+      w_l[warp * 16 + g + 8 * r] = l_run[r];
+    }
   }
   __syncthreads();
   for (int idx = tid; idx < G * HD; idx += NTHREADS) {
@@ -386,7 +408,7 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
 }
 
-template <int HD>
+template <int HD, bool LOW>
 int launch(const DkAttnParams& pin, cudaStream_t stream) {
   DkAttnParams p = pin;
   // entries (pages) one block can be given: the widest request split evenly
@@ -400,7 +422,7 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
   const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return DK_ERR_LAUNCH;
@@ -408,7 +430,7 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     configured = smem;
   }
   dim3 grid(p.splits, p.KV, p.rows);
-  attention_decode_kernel<HD><<<grid, NTHREADS, smem, stream>>>(p);
+  attention_decode_kernel<HD, LOW><<<grid, NTHREADS, smem, stream>>>(p);
   int rc = dk_check_launch("attention_decode");
   if (rc != 0 || p.splits == 1) return rc;
   dim3 mgrid(p.H, p.rows);
@@ -446,7 +468,9 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
   DK_REQUIRE(p.q_stride % 2 == 0, "attention_decode: q stride must be even");
   DK_REQUIRE(p.sel_pages == nullptr || (p.sel_count != nullptr && p.row_flags != nullptr && p.row_slot != nullptr),
              "attention_decode: chosen pages are given without their counts, row flags or slots");
-  return p.hd == 64 ? launch<64>(p, stream) : launch<128>(p, stream);
+  const bool low = p.H / p.KV <= 8;
+  if (p.hd == 64) return low ? launch<64, true>(p, stream) : launch<64, false>(p, stream);
+  return low ? launch<128, true>(p, stream) : launch<128, false>(p, stream);
 }
 
 // --------------------------------------------------------------------------------------

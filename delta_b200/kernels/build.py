@@ -24,7 +24,7 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_NAME = "libdelta_b200.so"
 # fast-math is never switched on: softmax, norms and the rotation are kept exact.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
-              "-Xcompiler", "-fPIC"]
+              "-Xcompiler", "-fPIC"] + os.environ.get("DELTA_B200_NVCC_EXTRA", "").split()
 
 
 class BuildError(RuntimeError):
