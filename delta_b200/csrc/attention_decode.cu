@@ -98,6 +98,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   if (p.row_filter == 1 && p.row_q_len[row] != 1) return;   // a row of a prompt: the prefill kernel's
   const RowInfo ri = row_info(p, row);
   const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(p.kv);
+  const float* rope = (p.fuse && p.rope_table) ? p.rope_table + (size_t)ri.pos * (HD / 2) * 2 : nullptr;
+  if (p.fuse && p.rope_table && ri.pos >= p.rope_positions) {
+    if (tid == 0) dk_report(p.err, DK_DEV_BAD_POSITION, ri.t, ri.pos, p.rope_positions);
+    return;
+  }
 
   // this block's share of the pages
   const int per = (ri.n_entries + p.splits - 1) / p.splits;
@@ -127,6 +132,35 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   }
   __syncthreads();
 
+  // Fused append: the block whose share ends with the request's newest page rotates the new
+  // token's key, writes key and value to that page, and only then starts to read pages.
+  if (p.fuse == 2 && e_end == ri.n_entries && e_end > e_begin) {
+    const int page = s_page[e_end - 1 - e_begin];
+    if (page >= 0 && s_lp[e_end - 1 - e_begin] == ri.pos / ps) {
+      const __nv_bfloat16* krow = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)ri.t * p.q_stride + (size_t)(p.H + kvh) * HD;
+      const __nv_bfloat16* vrow = krow + (size_t)p.KV * HD;
+      __nv_bfloat16* cache = const_cast<__nv_bfloat16*>(kv);
+      const size_t base = ((((size_t)page * 2 + 0) * p.KV + kvh) * ps + ri.pos % ps) * HD;
+      if (tid < HD / 2) {
+        const float a = __bfloat162float(krow[tid]), b = __bfloat162float(krow[tid + HD / 2]);
+        float c = 1.f, sn = 0.f;
+        if (rope) {
+          c = rope[2 * tid];
+          sn = rope[2 * tid + 1];
+        }
+        cache[base + tid] = __float2bfloat16_rn(a * c - b * sn);
+        cache[base + tid + HD / 2] = __float2bfloat16_rn(a * sn + b * c);
+      } else if (tid < HD / 2 + HD / 8) {
+        const int v8 = tid - HD / 2;
+        *reinterpret_cast<uint4*>(cache + base + (size_t)p.KV * ps * HD + v8 * 8) = *reinterpret_cast<const uint4*>(vrow + v8 * 8);
+      }
+    } else if (tid == 0) {
+      dk_report(p.err, DK_DEV_BAD_PAGE, ri.t, ri.pos / ps, page);
+    }
+    __threadfence();
+    __syncthreads();
+  }
+
   // the query heads of this group as A fragments: rows g and g + 8
   uint32_t qa[KB][4];
   {
@@ -138,6 +172,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
       qa[kb][1] = (!LOW && g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c) : 0u;
       qa[kb][2] = g < G ? *reinterpret_cast<const uint32_t*>(q + (size_t)g * HD + c + 8) : 0u;
       qa[kb][3] = (!LOW && g + 8 < G) ? *reinterpret_cast<const uint32_t*>(q + (size_t)(g + 8) * HD + c + 8) : 0u;
+    }
+    if (rope) {
+      // pairs (j, j + HD/2): the partner of a fragment of k-block kb sits in k-block kb + KB/2, same register
+#pragma unroll
+      for (int kb = 0; kb < KB / 2; ++kb) {
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {           // registers 0,1 (dims c, c+1) and 2,3 (dims c+8, c+9)
+          const int j = kb * 16 + 2 * tq + hi * 8;
+          const float4 cs = *reinterpret_cast<const float4*>(rope + 2 * j);   // cos j, sin j, cos j+1, sin j+1
+#pragma unroll
+          for (int r = 0; r < (LOW ? 1 : 2); ++r) {
+            __nv_bfloat162 a2 = *reinterpret_cast<__nv_bfloat162*>(&qa[kb][2 * hi + r]);
+            __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&qa[kb + KB / 2][2 * hi + r]);
+            const float a0 = __low2float(a2), a1 = __high2float(a2), b0 = __low2float(b2), b1 = __high2float(b2);
+            a2 = __floats2bfloat162_rn(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
+            b2 = __floats2bfloat162_rn(a0 * cs.y + b0 * cs.x, a1 * cs.w + b1 * cs.z);
+            qa[kb][2 * hi + r] = *reinterpret_cast<uint32_t*>(&a2);
+            qa[kb + KB / 2][2 * hi + r] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+        }
+      }
     }
   }
   // What does not change from tile to tile is worked out once: which key of a tile each of this
@@ -466,6 +521,10 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
   DK_REQUIRE(p.splits >= 1 && p.splits <= 65535 && p.KV <= 65535 && p.rows <= 65535, "attention_decode: grid too large");
   DK_REQUIRE(p.splits == 1 || p.scratch != nullptr, "attention_decode: %d splits need a scratch buffer", p.splits);
   DK_REQUIRE(p.q_stride % 2 == 0, "attention_decode: q stride must be even");
+  DK_REQUIRE(p.fuse >= 0 && p.fuse <= 2, "attention_decode: fuse must be 0, 1 or 2");
+  DK_REQUIRE(p.fuse == 0 || p.q_stride >= (p.H + 2 * p.KV) * p.hd,
+             "attention_decode: with fuse the query rows must be [q | k | v] rows of width %d, the stride is %d", (p.H + 2 * p.KV) * p.hd, p.q_stride);
+  DK_REQUIRE(p.fuse == 0 || p.rope_table == nullptr || p.rope_positions > 0, "attention_decode: a rope table without rows");
   DK_REQUIRE(p.sel_pages == nullptr || (p.sel_count != nullptr && p.row_flags != nullptr && p.row_slot != nullptr),
              "attention_decode: chosen pages are given without their counts, row flags or slots");
   const bool low = p.H / p.KV <= 8;

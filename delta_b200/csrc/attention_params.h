@@ -21,10 +21,14 @@ struct DkAttnParams {
   float* lse;              // [T, H] log-sum-exp of each (token, head); or null
   void* scratch;           // partial results of kernels that split the keys; or null
   int* err;                // device error record, 4 ints; or null
+  const float* rope_table; // decode kernel with fuse != 0: cos/sin [positions, hd/2, 2]; null: no rotation
   int T, rows, H, KV, hd, ps, max_pages, num_pages;
   int q_stride, window, sel_stride, dump_stride, dtype, splits;
   float scale;
   int block_entries;       // set by the launchers: pages one block keeps in shared memory
   int row_filter;          // 0: every row; 1: only rows that bring one token; 2: only rows that bring more
+  int fuse;                // decode kernel: q points into rows [q | k | v] that are not rotated yet; the kernel rotates
+                           // q and k itself and (fuse == 2) appends k and v of the new token to its page
+  int rope_positions;      // rows of rope_table
   int reserved;
 };

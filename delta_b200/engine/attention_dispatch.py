@@ -25,6 +25,13 @@ def decode_splits(rows: int, kv_heads: int, max_keys: int) -> int:
     return max(1, min(want, tiles, MAX_SPLITS))
 
 
+def can_fuse_rope_append(ctx, H: int, KV: int, hd: int, ps: int, interleaved: bool) -> bool:
+    """True when the step goes to the decode kernel, which can then rotate q and k and append the
+    new token's k and v itself; the separate rotary/append kernel is left out."""
+    return (ctx.decode_only and not ctx.plain_attention and ctx.dtype == torch.bfloat16 and not interleaved
+            and ops.attention_decode_supported(ctx.dtype, H, KV, hd, ps))
+
+
 def _decode(ctx, params, row_filter: int) -> None:
     max_keys = ctx.max_seq_len if not params.window else min(ctx.max_seq_len, params.window + params.ps)
     splits = ctx.fixed_decode_splits or decode_splits(ctx.num_rows, params.KV, max_keys)

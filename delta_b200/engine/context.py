@@ -80,6 +80,10 @@ class StepContext:
             self._scratch_pool[key] = buf
         return buf[:n].view(*shape)
 
+    def can_fuse_rope_append(self, H, KV, hd, ps, interleaved) -> bool:
+        from . import attention_dispatch
+        return attention_dispatch.can_fuse_rope_append(self, H, KV, hd, ps, interleaved)
+
     def attention(self, params) -> None:
         """Runs paged attention with the kernel that fits the batch."""
         from . import attention_dispatch

@@ -29,10 +29,10 @@ class AttnParams(C.Structure):
     _fields_ = [
         ("q", P), ("out", P), ("kv", P), ("block_table", P), ("tok_row", P), ("tok_pos", P),
         ("row_slot", P), ("row_flags", P), ("row_q_start", P), ("row_q_len", P), ("row_pos_start", P),
-        ("sel_pages", P), ("sel_count", P), ("dump", P), ("lse", P), ("scratch", P), ("err", P),
+        ("sel_pages", P), ("sel_count", P), ("dump", P), ("lse", P), ("scratch", P), ("err", P), ("rope_table", P),
         ("T", I), ("rows", I), ("H", I), ("KV", I), ("hd", I), ("ps", I), ("max_pages", I), ("num_pages", I),
         ("q_stride", I), ("window", I), ("sel_stride", I), ("dump_stride", I), ("dtype", I), ("splits", I),
-        ("scale", F), ("block_entries", I), ("row_filter", I), ("reserved", I),
+        ("scale", F), ("block_entries", I), ("row_filter", I), ("fuse", I), ("rope_positions", I), ("reserved", I),
     ]
 
 

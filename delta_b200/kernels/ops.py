@@ -138,7 +138,8 @@ def gemm_nt_plain(a, w, out):
 
 def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, KV, hd, ps, scale, row_slot=None,
                      row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None, sel_pages=None,
-                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0, row_filter=0) -> AttnParams:
+                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0, row_filter=0,
+                     fuse=0, rope_table=None) -> AttnParams:
     p = AttnParams()
     i32 = torch.int32
     p.q = _ptr(q, "q")
@@ -172,6 +173,9 @@ def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, 
     p.dtype = dtype_code(q.dtype)
     p.splits = splits
     p.row_filter = row_filter
+    p.fuse = fuse
+    p.rope_table = _ptr(rope_table, "rope_table", torch.float32)
+    p.rope_positions = rope_table.shape[0] if rope_table is not None else 0
     p.scale = float(scale)
     return p
 

@@ -91,8 +91,10 @@ class GQAAttention(Mixer):
         qkv = linear.linear(ctx, x, self.w_qkv)
         table = self.position.table(x.device) if self.position is not None else None
         interleaved = bool(getattr(self.position, "interleaved", False))
-        ops.rope_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.kv if cache.writes else None, table,
-                        H, KV, hd, cache.page_size, interleaved, err=ctx.err)
+        fuse = ctx.can_fuse_rope_append(H, KV, hd, cache.page_size, interleaved)
+        if not fuse:
+            ops.rope_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.kv if cache.writes else None, table,
+                            H, KV, hd, cache.page_size, interleaved, err=ctx.err)
         out = torch.empty((T, H * hd), dtype=x.dtype, device=x.device)
         selective = self.role != "full" and ctx.any_selective
         dump = lse = None
@@ -105,7 +107,8 @@ class GQAAttention(Mixer):
             row_flags=ctx.row_flags, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_pos_start=ctx.row_pos_start,
             sel_pages=ctx.state(SELECTED_PAGES) if (self.role == "subset" and selective) else None,
             sel_count=ctx.state(SELECTED_COUNT) if (self.role == "subset" and selective) else None,
-            dump=dump, lse=lse, err=ctx.err, window=self.window or 0)
+            dump=dump, lse=lse, err=ctx.err, window=self.window or 0,
+            fuse=(2 if cache.writes else 1) if fuse else 0, rope_table=table if fuse else None)
         ctx.attention(params)
         if self.role == "planner" and selective:
             scores = ctx.scratch("delta.page_scores", (ctx.num_rows, ctx.max_pages), torch.float32)

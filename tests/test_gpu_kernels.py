@@ -392,6 +392,47 @@ def test_attention_prefill_against_plain(H, KV, hd, ps):
     assert torch.allclose(out3.float().cpu(), refw, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (3, 2, 64, 8), (16, 1, 128, 32)])
+def test_attention_decode_fused_rope_and_append(G, KV, hd, ps):
+    """The decode kernel that rotates q and k and appends the new token itself against the
+    separate rotary/append kernel followed by the plain decode kernel: same cache, same output."""
+    from delta_b200.parts.rope import RotaryPositions
+    o = ops()
+    H = G * KV
+    dtype = torch.bfloat16
+    seq_lens = [1, ps, ps + 1, 64, 65, 300, 777]          # the new token opens a page, ends one, sits inside one
+    B = len(seq_lens)
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, [1] * B, seed=G)
+    table = RotaryPositions(hd, 5000000.0, 1024).table(torch.device(DEV))
+    qkv = torch.randn(B, (H + 2 * KV) * hd, device=DEV).to(dtype)
+    for b, n in enumerate(seq_lens):                       # the newest key and value are not in the cache yet
+        page = int(case.bt[b, (n - 1) // ps])
+        case.kv[page, :, :, (n - 1) % ps] = 0
+    def params(out, kv, **kw):
+        return o.make_attn_params(q=qkv_in, q_stride=qkv.shape[1], out=out, kv=kv, block_table=case.bt, tok_row=case.tok_row,
+                                  tok_pos=case.tok_pos, H=H, KV=KV, hd=hd, ps=ps, scale=1.0 / math.sqrt(hd), row_slot=case.row_slot,
+                                  row_q_start=case.row_q_start, row_q_len=case.row_q_len, row_pos_start=case.row_pos_start, **kw)
+    for splits in (1, 4):
+        scratch = torch.zeros(max(1, o.attention_decode_scratch_floats(B, H, hd, splits)), device=DEV)
+        # separate kernels
+        qkv_in, kv_a = qkv.clone(), case.kv.clone()
+        o.rope_append(qkv_in, case.tok_pos, case.tok_row, case.bt, kv_a, table, H, KV, hd, ps, False)
+        want = torch.zeros(B, H * hd, dtype=dtype, device=DEV)
+        o.attention_decode(params(want, kv_a, scratch=scratch, splits=splits))
+        # fused
+        qkv_in, kv_b = qkv.clone(), case.kv.clone()
+        got = torch.zeros_like(want)
+        o.attention_decode(params(got, kv_b, scratch=scratch, splits=splits, fuse=2, rope_table=table))
+        assert torch.equal(kv_a, kv_b), f"splits={splits}: the caches differ"
+        assert torch.equal(got, want), f"splits={splits}"
+        assert torch.equal(qkv_in, qkv)                    # the fused kernel leaves its input rows alone
+        # fuse=1 rotates q but appends nothing (a layer that reads another layer's cache)
+        kv_c = kv_a.clone()
+        got1 = torch.zeros_like(want)
+        o.attention_decode(params(got1, kv_c, scratch=scratch, splits=splits, fuse=1, rope_table=table))
+        assert torch.equal(kv_c, kv_a) and torch.equal(got1, want)
+
+
 @pytest.mark.parametrize("kernel", ["plain", "decode"])
 def test_attention_on_chosen_pages_and_score_dump(kernel):
     """Rows flagged for selection read only their chosen pages; a planner's dump holds the
