@@ -128,6 +128,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
+    ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
+    ap.add_argument("--subset_cache_size", type=int, default=64)
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -151,7 +154,10 @@ def main() -> int:
     max_b = 64 if not args.skip_points else args.batch
     eng = LMBackend(dtype=torch.bfloat16, device="cuda:0", cuda_graph_decode=not args.no_graph)
     eng.load_model(config_json=cfg, seed=0)
-    eng.setup_caches(max_batch_size=max(max_b, args.batch), max_seq_length=ctx_len, page_size=16, max_tokens_per_step=2048)
+    eng.setup_caches(max_batch_size=max(max_b, args.batch), max_seq_length=ctx_len, page_size=16, max_tokens_per_step=2048,
+                     enable_selective_cache=args.enable_selective_cache,
+                     full_cache_layers=args.full_cache_layers if args.enable_selective_cache else None,
+                     subset_cache_size=args.subset_cache_size)
     gen = torch.Generator().manual_seed(1)
 
     def fresh_prompts(n, length):
@@ -228,7 +234,7 @@ def main() -> int:
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": args.batch, "seq_len": ctx_len, "page_size": 16, "parallelism": "single GPU",
-                   "cuda_graph_decode": not args.no_graph, "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
+                   "cuda_graph_decode": not args.no_graph, "selective_cache": bool(args.enable_selective_cache), "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
                    "peaks": pk["source"]},
         "e2e": {"value": args.batch / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * args.steps)),
