@@ -1,0 +1,415 @@
+// Paged prefill attention on the fifth-generation tensor cores (tcgen05), bfloat16: rows that
+// bring more than one token (portions of prompts), causal, over the block table.
+//
+// A block owns 128 queries of one head; keys and values of the row's pages come in tiles of
+// 128 keys.  Both products run as tcgen05.mma with the accumulators in tensor memory (TMEM):
+//
+//   S = Q K^T      A = Q [128 x hd] and B = K [128 keys x hd] from shared memory, both
+//                  K-major; S[128 x 128] float in TMEM
+//   O += P V       A = P [128 x 128 keys] bfloat16 read from TMEM, where the softmax threads
+//                  wrote it over the scores it was made from; B = V [128 keys x hd] from
+//                  shared memory exactly as it lies in the cache (hd contiguous), read
+//                  "MN-major"; O[128 x hd] float stays in TMEM
+//
+// Tiles alternate between two halves of the block that do not wait for each other.  Half w
+// (softmax warps 4w..4w+3, score buffer w, accumulator O_w) takes tiles w, w + 2, ...; it keeps
+// a running maximum and sum of its own, and the two accumulators are merged at the end like
+// the partial results of a split softmax.  So while one half exponentiates, the other reads
+// its scores or waits for them, and the tensor cores always have the next product to do.
+//
+//   warps 0-7   softmax: thread r of a half owns query r, which is lane r of the TMEM, so a
+//               row's maximum and sum need no exchange between threads.  Two passes over the
+//               row in TMEM: the maximum; then exponentials, their sum, and P.  O_w is rescaled
+//               in TMEM only when the row maximum grew by more than 2^8 since it was last
+//               fixed (below that the old maximum stays in use, which changes nothing but the
+//               common factor of P and the sum).
+//   warps 8, 9  producers, one for K and one for V: they look the tile's pages up in the
+//               block table and ask TMA for one box [page x 64] per page and half of the head
+//               (128-byte swizzle), into rings of their own
+//   warp 10     one thread issues the MMAs in the order S(0) S(1) | PV(0) S(2) | PV(1) S(3) ...:
+//               S(j + 2) overwrites the buffer that P(j) was read from, which the in-order
+//               tensor pipe allows
+//
+// The queries' own keys were appended before this kernel runs, so a portion of a prompt
+// attends to the cache and to itself alike.  Pages past a row's last one are replaced by the
+// tile's first page: their scores are masked, and what is multiplied by the zeros is then
+// finite.  Every wait is bounded; when one gives up the block records it, stores nothing,
+// frees its tensor memory and returns.
+#include "common.cuh"
+#include "attention_params.h"
+#include "tcgen05_helpers.cuh"
+
+namespace {
+constexpr int QT = 128;            // queries per block (rows of both MMAs)
+constexpr int KT = 128;            // keys per tile
+constexpr int HALF_THREADS = 128;  // softmax threads of one half
+constexpr int PRODUCER_WARP0 = 8, MMA_WARP = 10;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int BOX_BYTES = 128 * 128;   // 128 rows of one 128-byte swizzle row each
+constexpr float RESCALE_STEP = 8.f;    // in powers of two
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0, COL_O = 2 * KT;   // S_0, S_1 (P_w lies over the first 64 columns of S_w), then O_0, O_1
+
+template <int HD>
+struct Layout {
+  static constexpr int HALVES = HD / 64;
+  static constexpr int STAGES = HD == 128 ? 2 : 4;
+  static constexpr int Q_BYTES = HALVES * BOX_BYTES;
+  static constexpr int TILE_BYTES = HALVES * BOX_BYTES;   // one K or V tile
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
+  static constexpr int TOTAL = OFF_V + STAGES * TILE_BYTES + 1024;    // 1024 to start on a swizzle boundary
+};
+
+// 2^x by the special-function unit (two units in the last place; results below 2^-126 become 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                          const __grid_constant__ CUtensorMap map_kv,
+                                                                          const DkAttnParams p) {
+  using L = Layout<HD>;
+  constexpr int STAGES = L::STAGES;
+  const int row = blockIdx.z, h = blockIdx.y;
+  const int q_len = p.row_q_len[row];
+  if (p.row_filter == 2 && q_len == 1) return;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // late tiles have the most keys: start them first
+  const int q0 = qt * QT;
+  if (q0 >= q_len) return;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // barriers: q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_full[2], p_full[2], o_done[2], merge
+  __shared__ __align__(8) unsigned long long bars[1 + 4 * 4 + 2 + 2 + 2 + 1];
+  __shared__ float2 row_stat[2][QT];   // [half][query]: maximum and sum of the half's tiles, for the merge
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int failed;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ps = p.ps, G = p.H / p.KV, kvh = h / G;
+  const int nq = min(QT, q_len - q0);
+  const int t0 = p.row_q_start[row] + q0;
+  const int pos0 = p.row_pos_start[row] + q0;
+  const int last_pos = pos0 + nq - 1;
+  const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int kt_first = lo / KT;
+  const int n_tiles = last_pos / KT - kt_first + 1;
+  const int last_page = last_pos / ps;
+
+  const uint32_t bar0 = s2u(&bars[0]);
+  const uint32_t q_full = bar0;
+  const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * 4, v_full = k_empty + 8 * 4, v_empty = v_full + 8 * 4;
+  const uint32_t s_full = v_empty + 8 * 4, p_full = s_full + 16, o_done = p_full + 16, merge_bar = o_done + 16;
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(v_empty + 8 * s, 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(s_full + 8 * w, 1);
+      mbar_init(p_full + 8 * w, HALF_THREADS);
+      mbar_init(o_done + 8 * w, 1);
+    }
+    mbar_init(merge_bar, 2 * HALF_THREADS);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == MMA_WARP) tmem_alloc(s2u(&tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t sm_q = s2u(smem + L::OFF_Q), sm_k = s2u(smem + L::OFF_K), sm_v = s2u(smem + L::OFF_V);
+
+  if (warp >= PRODUCER_WARP0 && warp < MMA_WARP) {
+    // ----------------------------------------------------------- producers
+    // one warp for K and one for V, so that the next K is never held up behind a V whose buffer
+    // is still being read
+    const int kind = warp - PRODUCER_WARP0;     // 0: K, 1: V
+    if (kind == 0 && lane == 0) {
+      mbar_expect_tx(q_full, (uint32_t)L::Q_BYTES);
+      for (int half = 0; half < L::HALVES; ++half)
+        tma_load_2d(sm_q + half * BOX_BYTES, &map_q, h * HD + half * 64, t0, q_full);   // rows past the last token are zeros
+    }
+    const int ppt = KT / ps;      // pages per tile, at most 16
+    const uint32_t full = kind ? v_full : k_full, empty = kind ? v_empty : k_empty, sm_dst = kind ? sm_v : sm_k;
+    int issued = 0;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % STAGES;
+      const int lp = (kt_first + j) * ppt + lane;
+      int page = -1;
+      if (lane < ppt && lp <= last_page && lp < p.max_pages) {
+        page = p.block_table[(size_t)row * p.max_pages + lp];
+        if (page < 0 || page >= p.num_pages) {
+          dk_report(p.err, DK_DEV_BAD_PAGE, row, lp, page);
+          page = -1;
+        }
+      }
+      int first = __shfl_sync(0xffffffffu, page, 0);
+      if (first < 0) first = 0;
+      if (page < 0) page = first;
+      const int grow = ((page * 2 + kind) * p.KV + kvh) * ps;    // row of the cache seen as [pages * 2 * KV * ps, hd]
+      bool ok = true;
+      if (j >= STAGES) ok = mbar_wait(empty + 8 * s, ((j / STAGES) - 1) & 1);
+      if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; break; }
+      if (lane == 0) mbar_expect_tx(full + 8 * s, (uint32_t)L::TILE_BYTES);
+      __syncwarp();
+      if (lane < ppt)
+        for (int half = 0; half < L::HALVES; ++half)
+          tma_load_2d(sm_dst + s * L::TILE_BYTES + half * BOX_BYTES + lane * ps * 128, &map_kv, half * 64, grow, full + 8 * s);
+      issued = j + 1;
+    }
+    if (failed && lane == 0) {
+      // nobody may leave while copies of this block are in flight: wait (bounded) for the last ones asked for
+      mbar_wait(q_full, 0);
+      for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(full + 8 * (j % STAGES), (j / STAGES) & 1);
+    }
+  } else if (warp == MMA_WARP) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc_bf16(QT, KT, false), idesc_o = instr_desc_bf16(QT, HD, true);
+      bool ok = mbar_wait(q_full, 0);
+      const uint64_t da0 = smem_desc_k_major(sm_q);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % STAGES, w = j & 1;
+        if (!mbar_wait(k_full + 8 * s, (j / STAGES) & 1)) return false;
+        tc_fence_after();
+        const uint64_t db0 = smem_desc_k_major(sm_k + s * L::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
+          umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(k_empty + 8 * s);
+        umma_commit(s_full + 8 * w);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (failed) { ok = false; break; }
+        const int s = j % STAGES, w = j & 1;
+        if (!mbar_wait(v_full + 8 * s, (j / STAGES) & 1) || !mbar_wait(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t dv0 = smem_desc_mn_major(sm_v + s * L::TILE_BYTES, BOX_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further down: two groups of 8 rows, 2048 bytes; 8 columns of P
+          umma_a_tmem(tmem + COL_O + w * HD, tmem + COL_S + w * KT + kk * 8, dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o,
+                      (j > 1 || kk > 0) ? 1u : 0u);
+        umma_commit(v_empty + 8 * s);
+        umma_commit(o_done + 8 * w);
+        if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }   // over the P just read: the pipe keeps the order
+      }
+      if (!ok) failed = 1;
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- softmax
+    const int w = warp >> 2;                            // which half: its tiles are w, w + 2, ...
+    const int r = (warp & 3) * 32 + lane;               // query of this thread = lane of the TMEM
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + COL_S + w * KT;    // scores of this half, and P over them
+    const uint32_t t_o = tmem + lane_base + COL_O + w * HD;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int qpos = pos0 + r;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool good = true;
+    int mine = 0;                                       // tiles of this half so far
+    for (int j = w; j < n_tiles; j += 2, ++mine) {
+      bool ok = mbar_wait(s_full + 8 * w, mine & 1);
+      if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; break; }
+      tc_fence_after();
+      const int kbase = (kt_first + j) * KT;
+      const bool edge = (kbase + KT - 1 > pos0) || (p.window > 0 && kbase < last_pos - p.window + 1);
+      // first pass over the row: its maximum
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one long one
+#pragma unroll 1
+      for (int c = 0; c < KT / 64; ++c) {
+        float v[64];
+        tmem_ld32_nowait(t_s + c * 64, v);
+        tmem_ld32_nowait(t_s + c * 64 + 32, v + 32);
+        tmem_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int kp = kbase + c * 64 + i;
+            if (!(kp <= qpos && (p.window <= 0 || kp > qpos - p.window))) v[i] = -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx4[0] = fmaxf(mx4[0], v[i]);
+          mx4[1] = fmaxf(mx4[1], v[i + 1]);
+          mx4[2] = fmaxf(mx4[2], v[i + 2]);
+          mx4[3] = fmaxf(mx4[3], v[i + 3]);
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_new = fmaxf(m_used, mx * sl2);
+      const bool grow = m_new > m_used + RESCALE_STEP;      // also the first finite maximum of a row
+      float factor = 1.f;
+      if (grow) {
+        factor = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_new);
+        m_used = m_new;
+      }
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      if (mine > 0 && __any_sync(0xffffffffu, grow)) {
+        ok = mbar_wait(o_done + 8 * w, (mine - 1) & 1);   // P V of this half's tile before is done: O_w is at rest
+        if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          float o[32];
+          tmem_ld32_nowait(t_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= factor;
+          tmem_st32(t_o + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      // second pass: exponentials, their sum, and P as bfloat16 pairs over the scores read so far
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int c = 0; c < KT / 32; ++c) {
+        float v[32];
+        tmem_ld32_nowait(t_s + c * 32, v);
+        tmem_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kp = kbase + c * 32 + i;
+            if (!(kp <= qpos && (p.window <= 0 || kp > qpos - p.window))) v[i] = -INFINITY;
+          }
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = fast_exp2(fmaf(v[2 * i], sl2, neg_m)), e1 = fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m));
+          sum4[(2 * i) & 3] += e0;
+          sum4[(2 * i + 1) & 3] += e1;
+          packed[i] = pack2(e0, e1);
+        }
+        tmem_st16(t_s + c * 16, packed);     // columns 16c..16c+15 held scores that are already used
+      }
+      l_sum = l_sum * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full + 8 * w);
+    }
+    if (good && mine > 0) {
+      bool ok = mbar_wait(o_done + 8 * w, (mine - 1) & 1);
+      if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; }
+    }
+    // merge of the two halves: each tells the other its maximum and sum, then writes half of the columns
+    row_stat[w][r] = make_float2(m_used, l_sum);
+    tc_fence_before();
+    mbar_arrive(merge_bar);
+    if (good) {
+      bool ok = mbar_wait(merge_bar, 0);
+      if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; }
+    }
+    if (good) {
+      tc_fence_after();
+      const float2 other = row_stat[w ^ 1][r];
+      const float m_all = fmaxf(m_used, other.x);
+      const float f_mine = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
+      const float f_other = other.x == -INFINITY ? 0.f : fast_exp2(other.x - m_all);
+      const float l_all = l_sum * f_mine + other.y * f_other;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      const float f0 = (w == 0 ? f_mine : f_other) * inv, f1 = (w == 0 ? f_other : f_mine) * inv;
+      const bool two = n_tiles > 1;                     // O_1 holds nothing when there was one tile
+      constexpr int OC = HD / 64;                       // chunks of 32 columns this thread writes
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)(t0 + r) * p.H + h) * HD + w * (HD / 2);
+#pragma unroll 1
+      for (int c = 0; c < OC; ++c) {
+        float o0[32], o1[32];
+        const uint32_t col = (uint32_t)(w * (HD / 2) + c * 32);
+        tmem_ld32_nowait(tmem + lane_base + COL_O + col, o0);
+        if (two) tmem_ld32_nowait(tmem + lane_base + COL_O + HD + col, o1);
+        tmem_wait_ld();
+        if (r < nq) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o0[i] = two ? o0[i] * f0 + o1[i] * f1 : o0[i] * f0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 st;
+            st.x = pack2(o0[v * 8], o0[v * 8 + 1]);
+            st.y = pack2(o0[v * 8 + 2], o0[v * 8 + 3]);
+            st.z = pack2(o0[v * 8 + 4], o0[v * 8 + 5]);
+            st.w = pack2(o0[v * 8 + 6], o0[v * 8 + 7]);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = st;
+          }
+        }
+      }
+      if (p.lse != nullptr && r < nq && w == 0)
+        p.lse[(size_t)(t0 + r) * p.H + h] = l_all > 0.f ? m_all * 0.6931471805599453f + logf(l_all) : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (failed && tid == 0) dk_report(p.err, DK_DEV_TIMEOUT, row, h, qt);
+  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+template <int HD>
+int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
+  using L = Layout<HD>;
+  CUtensorMap map_q, map_kv;
+  const long long kv_rows = (long long)p.num_pages * 2 * p.KV * p.ps;
+  DK_REQUIRE(kv_rows < (1ll << 31), "attention_prefill_tc: the cache of one layer has too many rows for a tensor map coordinate");
+  DK_REQUIRE(make_tensor_map_bf16(&map_q, p.q, p.T, p.H * HD, p.q_stride, QT),
+             "attention_prefill_tc: cannot encode the tensor map of the queries");
+  DK_REQUIRE(make_tensor_map_bf16(&map_kv, p.kv, kv_rows, HD, HD, p.ps),
+             "attention_prefill_tc: cannot encode the tensor map of the cache");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) {
+      dk_set_error("attention_prefill_tc: cannot get %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  dim3 grid((max_q_len + QT - 1) / QT, p.H, p.rows);
+  attention_prefill_tc_kernel<HD><<<grid, THREADS, L::TOTAL, stream>>>(map_q, map_kv, p);
+  return dk_check_launch("attention_prefill_tc");
+}
+}  // namespace
+
+extern "C" int dk_attention_prefill_tc_supported(int dtype, int H, int KV, int hd, int ps, int q_stride) {
+  if (dtype != DK_BF16 || KV <= 0 || H % KV != 0) return 0;
+  if (hd != 64 && hd != 128) return 0;
+  if (ps != 8 && ps != 16 && ps != 32 && ps != 64 && ps != 128) return 0;
+  if (q_stride % 8 != 0) return 0;
+  return 1;
+}
+
+// max_q_len: the most tokens any row brings (sizes the grid).
+extern "C" int dk_attention_prefill_tc(const DkAttnParams* pp, int max_q_len, cudaStream_t stream) {
+  const DkAttnParams& p = *pp;
+  if (p.T == 0 || p.rows == 0) return 0;
+  DK_REQUIRE(dk_attention_prefill_tc_supported(p.dtype, p.H, p.KV, p.hd, p.ps, p.q_stride),
+             "attention_prefill_tc: sizes not taken (bfloat16, head size 64 or 128, page size 8 to 128 and a power of two, "
+             "query stride a multiple of 8): dtype=%d H=%d KV=%d hd=%d ps=%d stride=%d", p.dtype, p.H, p.KV, p.hd, p.ps, p.q_stride);
+  DK_REQUIRE(max_q_len >= 1, "attention_prefill_tc: max_q_len must be positive");
+  DK_REQUIRE(p.scale > 0.f, "attention_prefill_tc: the scale of the scores must be positive");
+  DK_REQUIRE(p.row_q_start && p.row_q_len && p.row_pos_start && p.block_table, "attention_prefill_tc: row tables are missing");
+  DK_REQUIRE(p.H <= 65535 && p.rows <= 65535, "attention_prefill_tc: grid too large");
+  DK_REQUIRE(((uintptr_t)p.q % 16) == 0 && ((uintptr_t)p.kv % 16) == 0 && ((uintptr_t)p.out % 16) == 0,
+             "attention_prefill_tc: queries, cache and output must start on 16-byte boundaries");
+  return p.hd == 64 ? launch<64>(p, max_q_len, stream) : launch<128>(p, max_q_len, stream);
+}

@@ -26,7 +26,7 @@
 // Every wait on an mbarrier is bounded: when it gives up the kernel records that in the
 // error record, skips its stores, frees its tensor memory and returns.
 #include "common.cuh"
-#include <cuda.h>
+#include "tcgen05_helpers.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -36,78 +36,6 @@ constexpr int TILE_ROWS = 128;   // rows of W per block (UMMA M)
 constexpr int KSTEP = 64;        // elements of K per TMA box: one 128-byte swizzle row
 constexpr int KSUB_MAX = 4;      // boxes per stage
 constexpr int TC_THREADS = 128;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
-
-#define DK_DEV_TIMEOUT 4
-
-__device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// false when the wait gave up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);         // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
-  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                         // 128-byte swizzle
-  return d;
-}
-// instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128
-__device__ __forceinline__ uint32_t instr_desc(int n) {
-  uint32_t d = 0;
-  d |= 1u << 4;                      // D is float
-  d |= 1u << 7;                      // A is bfloat16
-  d |= 1u << 10;                     // B is bfloat16
-  d |= (uint32_t)(n >> 3) << 17;     // N / 8
-  d |= (uint32_t)(TILE_ROWS >> 4) << 24;   // M / 16
-  return d;
-}
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 struct TcArgs {
   void* out;         // [M, ldc] bfloat16 or float
@@ -160,8 +88,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {   // one warp allocates the tensor memory for the accumulator
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s2u(&tmem_base_slot)), "r"(a.tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    tmem_alloc(s2u(&tmem_base_slot), a.tmem_cols);
   }
   tc_fence_before();
   __syncthreads();
@@ -192,7 +119,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     }
   } else if (tid == 32) {
     // MMA issuer
-    const uint32_t idesc = instr_desc(a.mpad);
+    const uint32_t idesc = instr_desc_bf16(TILE_ROWS, a.mpad);
     for (int i = 0; i < n_steps; ++i) {
       const int s = i % a.stages;
       if (!mbar_wait(full0 + 8 * s, (i / a.stages) & 1)) {
@@ -202,7 +129,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
       tc_fence_after();
       const uint32_t sa = s2u(smem + (size_t)s * stage_bytes);
       for (int sub = 0; sub < KSUB; ++sub) {
-        const uint64_t da = smem_desc(sa + sub * a_bytes), db = smem_desc(sa + KSUB * a_bytes + sub * b_bytes);
+        const uint64_t da = smem_desc_k_major(sa + sub * a_bytes), db = smem_desc_k_major(sa + KSUB * a_bytes + sub * b_bytes);
 #pragma unroll
         for (int k = 0; k < KSTEP / 16; ++k)
           umma(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || sub > 0 || k > 0) ? 1u : 0u);
@@ -258,35 +185,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   }
   if (splits > 1) cluster.sync(); else __syncthreads();   // nobody leaves while its memory is still read
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    tmem_dealloc(tmem_base, a.tmem_cols);
   }
 }
 
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) return nullptr;
-  fn = (EncodeFn)p;
-  return fn;
-}
-
-// 2-D bfloat16 tensor [rows, K] with leading size ld: boxes of [box_rows x 64], 128-byte swizzle
 bool make_map(CUtensorMap* m, const void* base, int rows, int K, int ld, int box_rows) {
-  EncodeFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)KSTEP, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return make_tensor_map_bf16(m, base, rows, K, ld, box_rows);
 }
 }  // namespace
 

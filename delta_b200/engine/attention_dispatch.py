@@ -1,9 +1,11 @@
 """Chooses the attention kernels for a batch.
 
 bfloat16 with head size 64 or 128: rows that bring one token go to the split-key decode
-kernel (at most 16 query heads per key-value head), rows that bring more go to the tiled
-prefill kernel; a mixed step launches both, each skipping the other's rows.  Everything
-else (32 bit, other head sizes) goes to the plain kernel, which takes every size.
+kernel (at most 16 query heads per key-value head), rows that bring more go to a tiled
+prefill kernel (tcgen05 with 128-query tiles when a row brings at least 32 tokens, else
+warp-level MMA with 64-query tiles); a mixed step launches both, each skipping the other's
+rows.  Everything else (32 bit, other head sizes) goes to the plain kernel, which takes
+every size.
 """
 from __future__ import annotations
 
@@ -43,31 +45,44 @@ def _decode(ctx, params, row_filter: int) -> None:
     ops.attention_decode(params)
 
 
+TC_PREFILL_MIN_TOKENS = 32   # below this a 128-query tile of the tcgen05 kernel is mostly padding
+
+
+def _prefill_kernel(ctx, params):
+    """The kernel for rows that bring several tokens: tcgen05 when some row brings enough of them
+    and the sizes fit it, else warp-level MMA; None when neither takes the sizes."""
+    tc = ops.attention_prefill_tc_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps, params.q_stride)
+    mma = ops.attention_prefill_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)
+    if tc and (ctx.max_q_len >= TC_PREFILL_MIN_TOKENS or not mma):
+        return ops.attention_prefill_tc
+    return ops.attention_prefill if mma else None
+
+
 def run(ctx, params) -> None:
     if ctx.plain_attention or ctx.dtype != torch.bfloat16:
         ops.attention_plain(params)
         return
     dec_ok = ops.attention_decode_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)
-    pre_ok = ops.attention_prefill_supported(ctx.dtype, params.H, params.KV, params.hd, params.ps)
+    prefill = _prefill_kernel(ctx, params)
     if ctx.decode_only:
         if dec_ok:
             _decode(ctx, params, 0)
         else:
             ops.attention_plain(params)
         return
-    if not pre_ok:
+    if prefill is None:
         ops.attention_plain(params)
         return
     singles = any(n == 1 for n in ctx.host["q_lens"])
     if not singles:
         params.row_filter = 0
-        ops.attention_prefill(params, ctx.max_q_len)
+        prefill(params, ctx.max_q_len)
     elif dec_ok:
         _decode(ctx, params, 1)
         params.row_filter = 2
-        ops.attention_prefill(params, ctx.max_q_len)
+        prefill(params, ctx.max_q_len)
     elif params.sel_pages is None and params.dump is None:
         params.row_filter = 0
-        ops.attention_prefill(params, ctx.max_q_len)
+        prefill(params, ctx.max_q_len)
     else:
         ops.attention_plain(params)

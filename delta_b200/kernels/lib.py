@@ -52,6 +52,8 @@ _SIGNATURES = {
     "dk_attention_decode_supported": [I, I, I, I, I],
     "dk_attention_prefill": [C.POINTER(AttnParams), I, P],
     "dk_attention_prefill_supported": [I, I, I, I, I],
+    "dk_attention_prefill_tc": [C.POINTER(AttnParams), I, P],
+    "dk_attention_prefill_tc_supported": [I, I, I, I, I, I],
     "dk_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_gemm_small_m_supported": [I, I, I, I],
     "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, P, P],

@@ -212,6 +212,18 @@ def attention_prefill(params: AttnParams, max_q_len: int):
     _l.check(_l.load().dk_attention_prefill(C.byref(params), int(max_q_len), _stream()), "attention_prefill")
 
 
+def attention_prefill_tc_supported(dtype, H, KV, hd, ps, q_stride) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    return bool(_l.load().dk_attention_prefill_tc_supported(BF16, H, KV, hd, ps, int(q_stride)))
+
+
+def attention_prefill_tc(params: AttnParams, max_q_len: int):
+    """The same rows as ``attention_prefill`` on the tcgen05 tensor cores: 128 queries a block,
+    accumulators in tensor memory, pages fetched by TMA."""
+    _l.check(_l.load().dk_attention_prefill_tc(C.byref(params), int(max_q_len), _stream()), "attention_prefill_tc")
+
+
 def gemm_small_m_supported(M, N, K, swiglu=False) -> bool:
     return bool(_l.load().dk_gemm_small_m_supported(M, N, K, int(swiglu)))
 

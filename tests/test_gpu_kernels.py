@@ -358,12 +358,17 @@ def test_attention_decode_against_plain(G, KV, hd, ps):
     assert torch.allclose(out.float().cpu(), refw, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
 @pytest.mark.parametrize("H, KV, hd, ps", [(8, 2, 128, 16), (3, 3, 64, 8), (4, 1, 64, 64), (32, 4, 128, 32)])
-def test_attention_prefill_against_plain(H, KV, hd, ps):
-    """The tiled tensor-core prefill kernel: whole prompts, portions that start inside a page,
-    tiles that end before a page does, single tokens left to the decode kernel."""
+def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
+    """The two tiled tensor-core prefill kernels (warp-level MMA with 64-query tiles; tcgen05 with
+    128-query tiles and accumulators in tensor memory): whole prompts, portions that start inside
+    a page, tiles that end before a page does, single tokens left to the decode kernel."""
     o = ops()
     dtype = torch.bfloat16
+    prefill = o.attention_prefill if kernel == "mma_sync" else o.attention_prefill_tc
+    if kernel == "tcgen05":
+        assert o.attention_prefill_tc_supported(dtype, H, KV, hd, ps, H * hd)
     seq_lens = [200, 129, 64, 300, 1000, 65, 1]
     q_lens = [200, 5, 64, 2, 37, 1, 1]
     case = PagedCase(dtype, H, KV, hd, ps, seq_lens, q_lens, seed=H + ps)
@@ -371,12 +376,14 @@ def test_attention_prefill_against_plain(H, KV, hd, ps):
     ref, ref_lse, _ = case.reference()
     out = torch.zeros(case.T, H * hd, dtype=dtype, device=DEV)
     lse = torch.zeros(case.T, H, device=DEV)
-    o.attention_prefill(case.params(out, lse=lse), max(q_lens))
+    err = o.new_error_record(DEV)
+    prefill(case.params(out, lse=lse, err=err), max(q_lens))
+    assert err.cpu().tolist() == [0, 0, 0, 0]
     assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
     assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
     # single tokens are skipped with row_filter 2 and taken by the decode kernel with row_filter 1
     out2 = torch.zeros_like(out)
-    o.attention_prefill(case.params(out2, row_filter=2), max(q_lens))
+    prefill(case.params(out2, row_filter=2), max(q_lens))
     singles = [sum(q_lens[:5]), sum(q_lens[:6])]
     assert out2[singles].abs().sum() == 0
     if H // KV <= 16:
@@ -387,9 +394,39 @@ def test_attention_prefill_against_plain(H, KV, hd, ps):
     assert torch.allclose(out2.float().cpu(), ref, atol=2e-2, rtol=2e-2)
     # a window whose edge lies inside a tile and inside a page
     out3 = torch.zeros_like(out)
-    o.attention_prefill(case.params(out3, window=ps + 7), max(q_lens))
+    prefill(case.params(out3, window=ps + 7), max(q_lens))
     refw, _, _ = case.reference(window=ps + 7)
     assert torch.allclose(out3.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+    # a window of several tiles, whose far edge lies inside a tile
+    out4 = torch.zeros_like(out)
+    prefill(case.params(out4, window=300), max(q_lens))
+    refw, _, _ = case.reference(window=300)
+    assert torch.allclose(out4.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+
+
+def test_attention_prefill_tc_long_rows_and_maximum_that_grows():
+    """The tcgen05 prefill kernel over many tiles: a long cached prefix, scores that grow along
+    the row (so the accumulators in tensor memory are rescaled more than once), and one far key
+    that outweighs everything after it."""
+    o = ops()
+    H, KV, hd, ps = 4, 2, 128, 16
+    seq_lens, q_lens = [1500, 700], [333, 700]
+    case = PagedCase(torch.bfloat16, H, KV, hd, ps, seq_lens, q_lens, seed=11)
+    # keys grow with their position in request 1: later tiles bring larger maxima
+    ramp = torch.linspace(0.2, 3.0, seq_lens[1])[:, None, None]
+    case.k[1] = (case.k[1].float() * ramp).to(torch.bfloat16)
+    for lp in range((seq_lens[1] + ps - 1) // ps):
+        cnt = min(ps, seq_lens[1] - lp * ps)
+        case.kv[case.bt[1, lp], 0, :, :cnt] = case.k[1][lp * ps:lp * ps + cnt].transpose(0, 1).to(DEV)
+    make_far_key_stand_out(case, 0, 1, 3)
+    ref, ref_lse, _ = case.reference()
+    out = torch.zeros(case.T, H * hd, dtype=torch.bfloat16, device=DEV)
+    lse = torch.zeros(case.T, H, device=DEV)
+    err = o.new_error_record(DEV)
+    o.attention_prefill_tc(case.params(out, lse=lse, err=err), max(q_lens))
+    assert err.cpu().tolist() == [0, 0, 0, 0]
+    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
 
 
 @pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (3, 2, 64, 8), (16, 1, 128, 32)])
