@@ -53,7 +53,7 @@ constexpr int COL_S = 0, COL_O = 2 * KT;   // S_0, S_1 (P_w lies over the first 
 template <int HD>
 struct Layout {
   static constexpr int HALVES = HD / 64;
-  static constexpr int STAGES = HD == 128 ? 2 : 4;
+  static constexpr int STAGES = 2;    // two, because a stage is freed by the barrier of the tile two before (see the producers)
   static constexpr int Q_BYTES = HALVES * BOX_BYTES;
   static constexpr int TILE_BYTES = HALVES * BOX_BYTES;   // one K or V tile
   static constexpr int OFF_Q = 0;
@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // barriers: q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_full[2], p_full[2], o_done[2], merge
-  __shared__ __align__(8) unsigned long long bars[1 + 4 * 4 + 2 + 2 + 2 + 1];
+  // barriers: q_full, k_full[2], v_full[2], s_full[2], p_full[2], o_done[2], merge
+  __shared__ __align__(8) unsigned long long bars[1 + 2 + 2 + 2 + 2 + 2 + 1];
   __shared__ float2 row_stat[2][QT];   // [half][query]: maximum and sum of the half's tiles, for the merge
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int failed;
@@ -108,15 +108,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 
   const uint32_t bar0 = s2u(&bars[0]);
   const uint32_t q_full = bar0;
-  const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * 4, v_full = k_empty + 8 * 4, v_empty = v_full + 8 * 4;
-  const uint32_t s_full = v_empty + 8 * 4, p_full = s_full + 16, o_done = p_full + 16, merge_bar = o_done + 16;
+  const uint32_t k_full = bar0 + 8, v_full = k_full + 16, s_full = v_full + 16, p_full = s_full + 16, o_done = p_full + 16,
+                 merge_bar = o_done + 16;
   if (tid == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(k_full + 8 * s, 1);
-      mbar_init(k_empty + 8 * s, 1);
       mbar_init(v_full + 8 * s, 1);
-      mbar_init(v_empty + 8 * s, 1);
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(s_full + 8 * w, 1);
@@ -145,7 +143,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         tma_load_2d(sm_q + half * BOX_BYTES, &map_q, h * HD + half * 64, t0, q_full);   // rows past the last token are zeros
     }
     const int ppt = KT / ps;      // pages per tile, at most 16
-    const uint32_t full = kind ? v_full : k_full, empty = kind ? v_empty : k_empty, sm_dst = kind ? sm_v : sm_k;
+    // A stage of K is free when the scores made from it are complete, a stage of V when the product
+    // with it is: the producers wait on the same barriers as the softmax threads (tile j of half
+    // j % 2 is that barrier's completion number j / 2).
+    const uint32_t full = kind ? v_full : k_full, done = kind ? o_done : s_full, sm_dst = kind ? sm_v : sm_k;
     int issued = 0;
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j % STAGES;
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       if (page < 0) page = first;
       const int grow = ((page * 2 + kind) * p.KV + kvh) * ps;    // row of the cache seen as [pages * 2 * KV * ps, hd]
       bool ok = true;
-      if (j >= STAGES) ok = mbar_wait(empty + 8 * s, ((j / STAGES) - 1) & 1);
+      if (j >= STAGES) ok = mbar_wait(done + 8 * (j & 1), ((j / 2) - 1) & 1);
       if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; break; }
       if (lane == 0) mbar_expect_tx(full + 8 * s, (uint32_t)L::TILE_BYTES);
       __syncwarp();
@@ -193,14 +194,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
           const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
           umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(k_empty + 8 * s);
         umma_commit(s_full + 8 * w);
         return true;
       };
       if (ok) ok = issue_s(0);
       if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (failed) { ok = false; break; }
         const int s = j % STAGES, w = j & 1;
         if (!mbar_wait(v_full + 8 * s, (j / STAGES) & 1) || !mbar_wait(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
         tc_fence_after();
@@ -209,7 +208,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further down: two groups of 8 rows, 2048 bytes; 8 columns of P
           umma_a_tmem(tmem + COL_O + w * HD, tmem + COL_S + w * KT + kk * 8, dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o,
                       (j > 1 || kk > 0) ? 1u : 0u);
-        umma_commit(v_empty + 8 * s);
         umma_commit(o_done + 8 * w);
         if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }   // over the P just read: the pipe keeps the order
       }
