@@ -180,40 +180,51 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     }
   } else if (warp == MMA_WARP) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop, so that descriptors and addresses stay warp-uniform; one
+    // elected lane issues.
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_s = instr_desc_bf16(QT, KT, false), idesc_o = instr_desc_bf16(QT, HD, true);
-      bool ok = mbar_wait(q_full, 0);
+      auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {     // the same answer in every lane
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+      };
+      bool ok = wait_all(q_full, 0);
       const uint64_t da0 = smem_desc_k_major(sm_q);
       auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES, w = j & 1;
-        if (!mbar_wait(k_full + 8 * s, (j / STAGES) & 1)) return false;
+        if (!wait_all(k_full + 8 * s, (j / STAGES) & 1)) return false;
         tc_fence_after();
         const uint64_t db0 = smem_desc_k_major(sm_k + s * L::TILE_BYTES);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
-          umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
+            umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(s_full + 8 * w);
         }
-        umma_commit(s_full + 8 * w);
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
       if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int s = j % STAGES, w = j & 1;
-        if (!mbar_wait(v_full + 8 * s, (j / STAGES) & 1) || !mbar_wait(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
+        if (!wait_all(v_full + 8 * s, (j / STAGES) & 1) || !wait_all(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
         tc_fence_after();
         const uint64_t dv0 = smem_desc_mn_major(sm_v + s * L::TILE_BYTES, BOX_BYTES);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further down: two groups of 8 rows, 2048 bytes; 8 columns of P
-          umma_a_tmem(tmem + COL_O + w * HD, tmem + COL_S + w * KT + kk * 8, dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o,
-                      (j > 1 || kk > 0) ? 1u : 0u);
-        umma_commit(o_done + 8 * w);
+          for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further down: two groups of 8 rows, 2048 bytes; 8 columns of P
+            umma_a_tmem(tmem + COL_O + w * HD, tmem + COL_S + w * KT + kk * 8, dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o,
+                        (j > 1 || kk > 0) ? 1u : 0u);
+          umma_commit(o_done + 8 * w);
+        }
+        __syncwarp();
         if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }   // over the P just read: the pipe keeps the order
       }
       if (!ok) failed = 1;
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------- softmax
     const int w = warp >> 2;                            // which half: its tiles are w, w + 2, ...
