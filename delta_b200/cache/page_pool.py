@@ -4,7 +4,8 @@ The reference's ``PageManager`` (DELTA/Engine/DELTA/scheduler.py:8-40) keeps a
 shuffled free list, pops from its tail, reshuffles on every free and silently
 ignores a page that is freed twice.  This pool hands pages out last-in
 first-out (a page given back is the next one used again, which is what the
-tests of page reuse want), can start from a seeded shuffle to scatter pages as
+tests of page reuse want; pages given back together come out again in their
+old order), can start from a seeded shuffle to scatter pages as
 the reference does, and treats a double free or a foreign page as an error.
 """
 from __future__ import annotations
@@ -51,12 +52,17 @@ class PagePool:
         return out
 
     def free(self, pages) -> None:
+        """Gives pages back.  They go on the stack in reverse, so that pages freed together are
+        handed out again in the order they had: a request's pages that followed one another in the
+        pool still do for the next request, and the prefill kernel fetches such a run with one copy."""
+        pages = list(pages)
         for p in pages:
             if not (0 <= p < self.num_pages):
                 raise ValueError(f"page {p} does not belong to this pool of {self.num_pages}")
             if not self._held[p]:
                 raise ValueError(f"page {p} is freed twice (or was never handed out)")
             self._held[p] = False
+        for p in reversed(pages):
             self._free.append(p)
 
     def check(self) -> None:

@@ -6,29 +6,30 @@
 //
 //   S = Q K^T      A = Q [128 x hd] and B = K [128 keys x hd] from shared memory, both
 //                  K-major; S[128 x 128] float in TMEM
-//   O += P V       A = P [128 x 128 keys] bfloat16 read from TMEM, where the softmax threads
-//                  wrote it over the scores it was made from; B = V [128 keys x hd] from
-//                  shared memory exactly as it lies in the cache (hd contiguous), read
+//   O += P V       A = P [128 x 128 keys] bfloat16 from shared memory, where the softmax threads
+//                  write it in the swizzled layout a TMA load would leave; B = V [128 keys x hd]
+//                  from shared memory exactly as it lies in the cache (hd contiguous), read
 //                  "MN-major"; O[128 x hd] float stays in TMEM
 //
 // Tiles alternate between two halves of the block that do not wait for each other.  Half w
-// (softmax warps 4w..4w+3, score buffer w, accumulator O_w) takes tiles w, w + 2, ...; it keeps
-// a running maximum and sum of its own, and the two accumulators are merged at the end like
-// the partial results of a split softmax.  So while one half exponentiates, the other reads
-// its scores or waits for them, and the tensor cores always have the next product to do.
+// (softmax warps 4w..4w+3, score buffer S_w, accumulator O_w, P buffer P_w) takes tiles w,
+// w + 2, ...; it keeps a running maximum and sum of its own, and the two accumulators are merged
+// at the end like the partial results of a split softmax.  So while one half exponentiates, the
+// other reads its scores or waits for them, and the tensor cores always have a product to do.
 //
 //   warps 0-7   softmax: thread r of a half owns query r, which is lane r of the TMEM, so a
-//               row's maximum and sum need no exchange between threads.  Two passes over the
-//               row in TMEM: the maximum; then exponentials, their sum, and P.  O_w is rescaled
-//               in TMEM only when the row maximum grew by more than 2^8 since it was last
-//               fixed (below that the old maximum stays in use, which changes nothing but the
-//               common factor of P and the sum).
-//   warps 8, 9  producers, one for K and one for V: they look the tile's pages up in the
-//               block table and ask TMA for one box [page x 64] per page and half of the head
-//               (128-byte swizzle), into rings of their own
-//   warp 10     one thread issues the MMAs in the order S(0) S(1) | PV(0) S(2) | PV(1) S(3) ...:
-//               S(j + 2) overwrites the buffer that P(j) was read from, which the in-order
-//               tensor pipe allows
+//               row's maximum and sum need no exchange between threads.  The row comes into
+//               registers in one round trip, and the score buffer is released at once, so that
+//               the scores of the half's next tile are computed while these are exponentiated.
+//               O_w is rescaled in TMEM only when the row maximum grew by more than 2^8 since it
+//               was last fixed (below that the old maximum stays in use, which changes nothing
+//               but the common factor of P and the sum).
+//   warps 8, 9  producers, one for K and one for V: they look the tile's pages up in the block
+//               table.  Pages that follow one another in the pool come as one TMA box per half
+//               of the head (a 4-D view of the cache: a run of pages of one head); otherwise
+//               one box [page x 64] per page and half, which costs the warp some 75 cycles a box.
+//   warp 10     issues the score products: S(0), S(1), then S(j + 2) when S(j) is in registers
+//   warp 11     issues P(j) V(j) when P(j) is written
 //
 // The queries' own keys were appended before this kernel runs, so a portion of a prompt
 // attends to the cache and to itself alike.  Pages past a row's last one are replaced by the
@@ -43,8 +44,8 @@ namespace {
 constexpr int QT = 128;            // queries per block (rows of both MMAs)
 constexpr int KT = 128;            // keys per tile
 constexpr int HALF_THREADS = 128;  // softmax threads of one half
-constexpr int PRODUCER_WARP0 = 8, MMA_WARP = 10;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int PRODUCER_WARP0 = 8, MMA_WARP = 10;   // warp 10 issues the score products, warp 11 the P V products
+constexpr int THREADS = (MMA_WARP + 2) * 32;
 constexpr int BOX_BYTES = 128 * 128;   // 128 rows of one 128-byte swizzle row each
 constexpr float RESCALE_STEP = 8.f;    // in powers of two
 constexpr int TMEM_COLS = 512;
@@ -59,7 +60,9 @@ struct Layout {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
-  static constexpr int TOTAL = OFF_V + STAGES * TILE_BYTES + 1024;    // 1024 to start on a swizzle boundary
+  static constexpr int OFF_P = OFF_V + STAGES * TILE_BYTES;           // P of each half: two boxes [128 x 64 keys]
+  static constexpr int P_BYTES = 2 * BOX_BYTES;
+  static constexpr int TOTAL = OFF_P + 2 * P_BYTES + 1024;            // 1024 to start on a swizzle boundary
 };
 
 // 2^x by the special-function unit (two units in the last place; results below 2^-126 become 0)
@@ -77,6 +80,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                           const __grid_constant__ CUtensorMap map_kv,
+                                                                          const __grid_constant__ CUtensorMap map_run,
                                                                           const DkAttnParams p) {
   using L = Layout<HD>;
   constexpr int STAGES = L::STAGES;
@@ -89,9 +93,11 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // barriers: q_full, k_full[2], v_full[2], s_full[2], p_full[2], o_done[2], merge
-  __shared__ __align__(8) unsigned long long bars[1 + 2 + 2 + 2 + 2 + 2 + 1];
-  __shared__ float2 row_stat[2][QT];   // [half][query]: maximum and sum of the half's tiles, for the merge
+  // barriers: q_full, k_full[2], v_full[2], s_full[2], p_full[2], o_done[2], merge, s_free[2]
+  __shared__ __align__(8) unsigned long long bars[1 + 2 + 2 + 2 + 2 + 2 + 1 + 2];
+  // row_stat(w)[query]: maximum and sum of half w's tiles, for the merge; it lies over the half's P, which
+  // is no longer read when the half has seen its last product complete
+  auto row_stat = [&](int w) { return reinterpret_cast<float2*>(smem + L::OFF_P + w * L::P_BYTES); };
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int failed;
 
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   const uint32_t bar0 = s2u(&bars[0]);
   const uint32_t q_full = bar0;
   const uint32_t k_full = bar0 + 8, v_full = k_full + 16, s_full = v_full + 16, p_full = s_full + 16, o_done = p_full + 16,
-                 merge_bar = o_done + 16;
+                 merge_bar = o_done + 16, s_free = merge_bar + 8;
   if (tid == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -120,6 +126,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       mbar_init(s_full + 8 * w, 1);
       mbar_init(p_full + 8 * w, HALF_THREADS);
       mbar_init(o_done + 8 * w, 1);
+      mbar_init(s_free + 8 * w, HALF_THREADS);
     }
     mbar_init(merge_bar, 2 * HALF_THREADS);
     failed = 0;
@@ -130,7 +137,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t sm_q = s2u(smem + L::OFF_Q), sm_k = s2u(smem + L::OFF_K), sm_v = s2u(smem + L::OFF_V);
+  const uint32_t sm_q = s2u(smem + L::OFF_Q), sm_k = s2u(smem + L::OFF_K), sm_v = s2u(smem + L::OFF_V),
+                 sm_p = s2u(smem + L::OFF_P);
 
   if (warp >= PRODUCER_WARP0 && warp < MMA_WARP) {
     // ----------------------------------------------------------- producers
@@ -160,6 +168,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         }
       }
       int first = __shfl_sync(0xffffffffu, page, 0);
+      // a tile whose pages follow one another in the pool comes with one request per half of the head
+      const bool run = __all_sync(0xffffffffu, lane >= ppt || (page >= 0 && page == first + lane));
       if (first < 0) first = 0;
       if (page < 0) page = first;
       const int grow = ((page * 2 + kind) * p.KV + kvh) * ps;    // row of the cache seen as [pages * 2 * KV * ps, hd]
@@ -168,9 +178,14 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; break; }
       if (lane == 0) mbar_expect_tx(full + 8 * s, (uint32_t)L::TILE_BYTES);
       __syncwarp();
-      if (lane < ppt)
+      if (run) {
+        if (lane == 0)
+          for (int half = 0; half < L::HALVES; ++half)
+            tma_load_4d(sm_dst + s * L::TILE_BYTES + half * BOX_BYTES, &map_run, half * 64, 0, kind * p.KV + kvh, first, full + 8 * s);
+      } else if (lane < ppt) {
         for (int half = 0; half < L::HALVES; ++half)
           tma_load_2d(sm_dst + s * L::TILE_BYTES + half * BOX_BYTES + lane * ps * 128, &map_kv, half * 64, grow, full + 8 * s);
+      }
       issued = j + 1;
     }
     if (failed && lane == 0) {
@@ -179,58 +194,64 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(full + 8 * (j % STAGES), (j / STAGES) & 1);
     }
   } else if (warp == MMA_WARP) {
-    // ---------------------------------------------------------- MMA issuer
+    // ------------------------------------------- MMA issuer of the scores
     // The whole warp runs the loop, so that descriptors and addresses stay warp-uniform; one
-    // elected lane issues.
-    {
-      const bool leader = elect_one();
-      const uint32_t idesc_s = instr_desc_bf16(QT, KT, false), idesc_o = instr_desc_bf16(QT, HD, true);
-      auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {     // the same answer in every lane
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity));
-      };
-      bool ok = wait_all(q_full, 0);
-      const uint64_t da0 = smem_desc_k_major(sm_q);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j % STAGES, w = j & 1;
-        if (!wait_all(k_full + 8 * s, (j / STAGES) & 1)) return false;
-        tc_fence_after();
-        const uint64_t db0 = smem_desc_k_major(sm_k + s * L::TILE_BYTES);
-        if (leader) {
+    // elected lane issues.  S(0) and S(1) at once, then S(j + 2) as soon as the softmax threads
+    // hold S(j) in registers (their half's score buffer is free then) and K(j + 2) has arrived.
+    const bool leader = elect_one();
+    const uint32_t idesc_s = instr_desc_bf16(QT, KT, false);
+    auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {     // the same answer in every lane
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+    };
+    bool ok = wait_all(q_full, 0);
+    const uint64_t da0 = smem_desc_k_major(sm_q);
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int s = j % STAGES, w = j & 1;
+      if (j >= 2 && !wait_all(s_free + 8 * w, ((j / 2) - 1) & 1)) { ok = false; break; }
+      if (!wait_all(k_full + 8 * s, (j / STAGES) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const uint64_t db0 = smem_desc_k_major(sm_k + s * L::TILE_BYTES);
+      if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
-            umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
-          }
-          umma_commit(s_full + 8 * w);
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t off = (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4);   // start addresses count 16 bytes
+          umma(tmem + COL_S + w * KT, da0 + off, db0 + off, idesc_s, kk > 0 ? 1u : 0u);
         }
-        __syncwarp();
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      if (ok && n_tiles > 1) ok = issue_s(1);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % STAGES, w = j & 1;
-        if (!wait_all(v_full + 8 * s, (j / STAGES) & 1) || !wait_all(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
-        tc_fence_after();
-        const uint64_t dv0 = smem_desc_mn_major(sm_v + s * L::TILE_BYTES, BOX_BYTES);
-        if (leader) {
-#pragma unroll
-          for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further down: two groups of 8 rows, 2048 bytes; 8 columns of P
-            umma_a_tmem(tmem + COL_O + w * HD, tmem + COL_S + w * KT + kk * 8, dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o,
-                        (j > 1 || kk > 0) ? 1u : 0u);
-          umma_commit(o_done + 8 * w);
-        }
-        __syncwarp();
-        if (j + 2 < n_tiles && !issue_s(j + 2)) { ok = false; break; }   // over the P just read: the pipe keeps the order
+        umma_commit(s_full + 8 * w);
       }
-      if (!ok) failed = 1;
+      __syncwarp();
     }
+    if (!ok) failed = 1;
+  } else if (warp == MMA_WARP + 1) {
+    // ------------------------------------------ MMA issuer of P V
+    const bool leader = elect_one();
+    const uint32_t idesc_o = instr_desc_bf16(QT, HD, true);
+    auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+    };
+    bool ok = true;
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int s = j % STAGES, w = j & 1;
+      if (!wait_all(v_full + 8 * s, (j / STAGES) & 1) || !wait_all(p_full + 8 * w, (j / 2) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const uint64_t dp0 = smem_desc_k_major(sm_p + w * L::P_BYTES);
+      const uint64_t dv0 = smem_desc_mn_major(sm_v + s * L::TILE_BYTES, BOX_BYTES);
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk)   // 16 keys further: 32 bytes along a row of P, two groups of 8 rows of V
+          umma(tmem + COL_O + w * HD, dp0 + (uint64_t)(((kk / 4) * BOX_BYTES + (kk % 4) * 32) >> 4),
+               dv0 + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j > 1 || kk > 0) ? 1u : 0u);
+        umma_commit(o_done + 8 * w);
+      }
+      __syncwarp();
+    }
+    if (!ok) failed = 1;
   } else {
     // ------------------------------------------------------------- softmax
     const int w = warp >> 2;                            // which half: its tiles are w, w + 2, ...
     const int r = (warp & 3) * 32 + lane;               // query of this thread = lane of the TMEM
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + COL_S + w * KT;    // scores of this half, and P over them
+    const uint32_t t_s = tmem + lane_base + COL_S + w * KT;    // scores of this half
     const uint32_t t_o = tmem + lane_base + COL_O + w * HD;
     const float sl2 = p.scale * 1.4426950408889634f;
     const int qpos = pos0 + r;
@@ -243,28 +264,28 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       tc_fence_after();
       const int kbase = (kt_first + j) * KT;
       const bool edge = (kbase + KT - 1 > pos0) || (p.window > 0 && kbase < last_pos - p.window + 1);
-      // first pass over the row: its maximum
+      // the whole row comes into registers in one round trip; the score buffer is free for the
+      // scores of this half's next tile at once
+      float v[KT];
+#pragma unroll
+      for (int c = 0; c < KT / 32; ++c) tmem_ld32_nowait(t_s + c * 32, v + c * 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(s_free + 8 * w);
+      if (edge) {
+#pragma unroll
+        for (int i = 0; i < KT; ++i) {
+          const int kp = kbase + i;
+          if (!(kp <= qpos && (p.window <= 0 || kp > qpos - p.window))) v[i] = -INFINITY;
+        }
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one long one
-#pragma unroll 1
-      for (int c = 0; c < KT / 64; ++c) {
-        float v[64];
-        tmem_ld32_nowait(t_s + c * 64, v);
-        tmem_ld32_nowait(t_s + c * 64 + 32, v + 32);
-        tmem_wait_ld();
-        if (edge) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int kp = kbase + c * 64 + i;
-            if (!(kp <= qpos && (p.window <= 0 || kp > qpos - p.window))) v[i] = -INFINITY;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          mx4[0] = fmaxf(mx4[0], v[i]);
-          mx4[1] = fmaxf(mx4[1], v[i + 1]);
-          mx4[2] = fmaxf(mx4[2], v[i + 2]);
-          mx4[3] = fmaxf(mx4[3], v[i + 3]);
-        }
+      for (int i = 0; i < KT; i += 4) {
+        mx4[0] = fmaxf(mx4[0], v[i]);
+        mx4[1] = fmaxf(mx4[1], v[i + 1]);
+        mx4[2] = fmaxf(mx4[2], v[i + 2]);
+        mx4[3] = fmaxf(mx4[3], v[i + 3]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * sl2);
@@ -275,48 +296,43 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         m_used = m_new;
       }
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-      if (mine > 0 && __any_sync(0xffffffffu, grow)) {
-        ok = mbar_wait(o_done + 8 * w, (mine - 1) & 1);   // P V of this half's tile before is done: O_w is at rest
+      if (mine > 0) {
+        // P V of this half's tile before is done: its P may be overwritten, and O_w is at rest
+        ok = mbar_wait(o_done + 8 * w, (mine - 1) & 1);
         if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; break; }
-        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+          tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          float o[32];
-          tmem_ld32_nowait(t_o + c * 32, o);
-          tmem_wait_ld();
+          for (int c = 0; c < HD / 32; ++c) {
+            float o[32];
+            tmem_ld32_nowait(t_o + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= factor;
-          tmem_st32(t_o + c * 32, o);
-        }
-        tmem_wait_st();
-      }
-      // second pass: exponentials, their sum, and P as bfloat16 pairs over the scores read so far
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-      for (int c = 0; c < KT / 32; ++c) {
-        float v[32];
-        tmem_ld32_nowait(t_s + c * 32, v);
-        tmem_wait_ld();
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kp = kbase + c * 32 + i;
-            if (!(kp <= qpos && (p.window <= 0 || kp > qpos - p.window))) v[i] = -INFINITY;
+            for (int i = 0; i < 32; ++i) o[i] *= factor;
+            tmem_st32(t_o + c * 32, o);
           }
+          tmem_wait_st();
+          tc_fence_before();
         }
-        uint32_t packed[16];
+      }
+      // exponentials, their sum, and P as bfloat16 in the layout a TMA load with 128-byte swizzle
+      // would leave: two boxes of 64 keys, rows of 128 bytes, 16-byte chunks exchanged by the row
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t p_row = sm_p + w * L::P_BYTES + r * 128;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float e0 = fast_exp2(fmaf(v[2 * i], sl2, neg_m)), e1 = fast_exp2(fmaf(v[2 * i + 1], sl2, neg_m));
-          sum4[(2 * i) & 3] += e0;
-          sum4[(2 * i + 1) & 3] += e1;
-          packed[i] = pack2(e0, e1);
+      for (int c = 0; c < KT / 8; ++c) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = fast_exp2(fmaf(v[c * 8 + i], sl2, neg_m));
+          sum4[i & 3] += e[i];
         }
-        tmem_st16(t_s + c * 16, packed);     // columns 16c..16c+15 held scores that are already used
+        const uint32_t addr = p_row + (c / 8) * BOX_BYTES + (((c % 8) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(pack2(e[0], e[1])), "r"(pack2(e[2], e[3])),
+                     "r"(pack2(e[4], e[5])), "r"(pack2(e[6], e[7])) : "memory");
       }
       l_sum = l_sum * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      tmem_wait_st();
-      tc_fence_before();
+      fence_async_smem();
       mbar_arrive(p_full + 8 * w);
     }
     if (good && mine > 0) {
@@ -324,7 +340,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       if (!__all_sync(0xffffffffu, ok && !failed)) { failed = 1; good = false; }
     }
     // merge of the two halves: each tells the other its maximum and sum, then writes half of the columns
-    row_stat[w][r] = make_float2(m_used, l_sum);
+    row_stat(w)[r] = make_float2(m_used, l_sum);
     tc_fence_before();
     mbar_arrive(merge_bar);
     if (good) {
@@ -333,7 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     }
     if (good) {
       tc_fence_after();
-      const float2 other = row_stat[w ^ 1][r];
+      const float2 other = row_stat(w ^ 1)[r];
       const float m_all = fmaxf(m_used, other.x);
       const float f_mine = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
       const float f_other = other.x == -INFINITY ? 0.f : fast_exp2(other.x - m_all);
@@ -377,13 +393,20 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 template <int HD>
 int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
   using L = Layout<HD>;
-  CUtensorMap map_q, map_kv;
+  CUtensorMap map_q, map_kv, map_run;
   const long long kv_rows = (long long)p.num_pages * 2 * p.KV * p.ps;
   DK_REQUIRE(kv_rows < (1ll << 31), "attention_prefill_tc: the cache of one layer has too many rows for a tensor map coordinate");
   DK_REQUIRE(make_tensor_map_bf16(&map_q, p.q, p.T, p.H * HD, p.q_stride, QT),
              "attention_prefill_tc: cannot encode the tensor map of the queries");
   DK_REQUIRE(make_tensor_map_bf16(&map_kv, p.kv, kv_rows, HD, HD, p.ps),
              "attention_prefill_tc: cannot encode the tensor map of the cache");
+  // the cache as [page][K|V, head][offset][hd]: a run of pages of one head in one box
+  const unsigned long long dims[4] = {(unsigned long long)HD, (unsigned long long)p.ps, (unsigned long long)(2 * p.KV),
+                                      (unsigned long long)p.num_pages};
+  const unsigned long long strides[3] = {(unsigned long long)HD * 2, (unsigned long long)p.ps * HD * 2,
+                                         (unsigned long long)2 * p.KV * p.ps * HD * 2};
+  DK_REQUIRE(make_tensor_map_bf16_4d(&map_run, p.kv, dims, strides, p.ps, KT / p.ps),
+             "attention_prefill_tc: cannot encode the tensor map of runs of pages");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -394,7 +417,7 @@ int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((max_q_len + QT - 1) / QT, p.H, p.rows);
-  attention_prefill_tc_kernel<HD><<<grid, THREADS, L::TOTAL, stream>>>(map_q, map_kv, p);
+  attention_prefill_tc_kernel<HD><<<grid, THREADS, L::TOTAL, stream>>>(map_q, map_kv, map_run, p);
   return dk_check_launch("attention_prefill_tc");
 }
 }  // namespace

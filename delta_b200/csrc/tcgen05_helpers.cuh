@@ -57,6 +57,11 @@ __device__ __forceinline__ bool elect_one() {
   asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
   return pred != 0;
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 // makes shared memory written with ordinary stores visible to the TMA and tensor-core units
@@ -182,6 +187,21 @@ static inline TensorMapEncodeFn tensor_map_encode_fn() {
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) return nullptr;
   fn = (TensorMapEncodeFn)p;
   return fn;
+}
+
+// 4-D bfloat16 tensor [d3][d2][d1][d0] (d0 contiguous) with byte strides s1, s2, s3: boxes of
+// [b3 x 1 x b1 x 64], 128-byte swizzle, zeros where a box reaches past the tensor
+static inline bool make_tensor_map_bf16_4d(CUtensorMap* m, const void* base, const unsigned long long dims[4],
+                                           const unsigned long long strides_bytes[3], int b1, int b3) {
+  TensorMapEncodeFn fn = tensor_map_encode_fn();
+  if (!fn) return false;
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t box[4] = {64u, (cuuint32_t)b1, 1u, (cuuint32_t)b3};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), d, st, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // 2-D bfloat16 tensor [rows, cols] with leading size ld: boxes of [box_rows x 64], 128-byte swizzle,

@@ -358,7 +358,7 @@ def test_attention_decode_against_plain(G, KV, hd, ps):
     assert torch.allclose(out.float().cpu(), refw, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_runs"])
 @pytest.mark.parametrize("H, KV, hd, ps", [(8, 2, 128, 16), (3, 3, 64, 8), (4, 1, 64, 64), (32, 4, 128, 32)])
 def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
     """The two tiled tensor-core prefill kernels (warp-level MMA with 64-query tiles; tcgen05 with
@@ -367,11 +367,13 @@ def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
     o = ops()
     dtype = torch.bfloat16
     prefill = o.attention_prefill if kernel == "mma_sync" else o.attention_prefill_tc
-    if kernel == "tcgen05":
+    if kernel != "mma_sync":
         assert o.attention_prefill_tc_supported(dtype, H, KV, hd, ps, H * hd)
     seq_lens = [200, 129, 64, 300, 1000, 65, 1]
     q_lens = [200, 5, 64, 2, 37, 1, 1]
-    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, q_lens, seed=H + ps)
+    # "runs": a request's pages follow one another in the pool, which the tcgen05 kernel fetches
+    # with one copy per tile; else the pages are scattered and fetched one by one
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, q_lens, seed=H + ps, scatter=kernel != "tcgen05_runs")
     make_far_key_stand_out(case, 4, 2, 0)            # the last query of request 4 looks far back
     ref, ref_lse, _ = case.reference()
     out = torch.zeros(case.T, H * hd, dtype=dtype, device=DEV)
