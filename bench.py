@@ -10,8 +10,13 @@ step.  It prints ONE JSON line:
 
   value      decoded tokens per second, device time of the K timed steps (model step
              and sampling, measured with CUDA events around each step)
-  e2e        the same through the Python entry point (LMBackend.step): every step
-             copies its inputs from pinned host memory and reads the new tokens back
+  e2e        the same through the Python entry point (LMBackend.step), timed over further runs
+             of K steps without the per-step synchronisation the device timing needs: every
+             step copies its inputs (positions, block tables, sampling parameters, tokens) from
+             pinned host memory and reads the new tokens back to the host.  ``value`` is the
+             engine as it runs by default: a decode step is launched while the host still reads
+             the step before, with its tokens taken from that step's result on the device;
+             ``value_tokens_fed_back_through_host`` is the same with that switched off
   prefill    one prompt of 2,048 tokens in one step; frac = flops / time / peak
   roofline   bytes a decode step has to read (every weight once, and the cache of the
              live requests) / its time, against the copy bandwidth
@@ -167,7 +172,7 @@ def main() -> int:
         """Prefills ``batch`` requests so that the timed decode steps end at the context
         length, then times ``steps`` decode steps.  Returns (device ms per step, end-to-end
         ms per step, launches per step, bytes in, bytes out, mean context)."""
-        total_new = warmup + steps + 1
+        total_new = warmup + 3 * steps + 3
         plen = ctx_len - total_new
         sch = eng.scheduler
         sch.decode_while_prefill = False
@@ -182,16 +187,27 @@ def main() -> int:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         eng.record_timings = True
         eng.step_timings.clear()
-        e0.record()
         for _ in range(steps):
             eng.step()
-        e1.record()
         torch.cuda.synchronize()
         eng.record_timings = False
-        e2e_ms = e0.elapsed_time(e1) / steps
         dev_ms = sum(s["model_forward_ms"] + s["postprocess_ms"] for s in eng.step_timings) / steps
         launches = (ops.launch_count() - l0) / steps
         mean_ctx = plen + warmup + steps / 2
+        # the same number of steps again as a user drives them: no per-step synchronisation for
+        # timing, so the engine launches each decode step while the host still reads the one before
+        e2e = []
+        for ahead in (False, True):     # tokens fed back through the host; then on the device, one step ahead
+            eng.run_ahead = ahead
+            eng.step()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                eng.step()
+            e1.record()
+            torch.cuda.synchronize()
+            e2e.append(e0.elapsed_time(e1) / steps)
+        e2e_ms = tuple(e2e)
         h2d = eng.runner.last_staging_bytes
         sch.abort_all("bench")
         return dev_ms, e2e_ms, launches, h2d, 4 * batch, mean_ctx
@@ -236,7 +252,8 @@ def main() -> int:
                    "global_batch": args.batch, "seq_len": ctx_len, "page_size": 16, "parallelism": "single GPU",
                    "cuda_graph_decode": not args.no_graph, "selective_cache": bool(args.enable_selective_cache), "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
                    "peaks": pk["source"]},
-        "e2e": {"value": args.batch / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": args.batch / (e2e_ms[1] / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "value_tokens_fed_back_through_host": args.batch / (e2e_ms[0] / 1e3)},
         "gpu_launches": int(round(launches * args.steps)),
         "clocks": clk,
         "prefill": prefill,

@@ -49,8 +49,13 @@ class LMBackend:
         self.tokenizer = None
         self.step_timings: List[dict] = []
         self.throughput_mode = False
-        self._host_tokens = None
+        self._host_tokens = [None, None]
+        self._read_turn = 0
         self.record_timings = False
+        # Decode steps are launched one step ahead of the host: while the host waits for the tokens
+        # of step N, step N + 1 already runs with those tokens taken on the device.  See _run_ahead.
+        self.run_ahead = True
+        self._ahead = None
 
     # ---- set-up -------------------------------------------------------------
     def load_model(self, model_dir=None, *, config_json: Optional[dict] = None, seed: Optional[int] = None, **unused):
@@ -114,46 +119,123 @@ class LMBackend:
         t0 = time.perf_counter()
         plan = sch.schedule()
         if not plan:
+            self._ahead = None
             if sch.has_work() and not sch.running:
                 # nothing runs and the head of the queue cannot be admitted: it never will be
                 r = sch.waiting.pop(0)
                 sch._fail(r, "cannot be admitted: not enough cache pages")
                 return [r]
             return []
-        rows = []
-        for x in plan:
-            r = x.request
-            toks = r.tokens[x.start:x.start + x.count]
-            rows.append(RowInput(r.slot, toks, x.start, [x.count - 1] if x.samples else [],
-                                 selective=bool(sch.selective and x.decode), sampling=r.sampling))
+        ahead, self._ahead = self._ahead, None
+        reuse = None if (ahead is None or self.record_timings) else self._match_ahead(plan, ahead)
         ev = None
-        if self.record_timings:
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-            ev[0].record()
-        logits, tokens = runner.step_and_sample(rows)
+        if reuse is not None:
+            # this step was launched while the host waited for the step before: only its result is read
+            tokens, read = ahead["tokens"], ahead["read"]
+        else:
+            rows = []
+            for x in plan:
+                r = x.request
+                toks = r.tokens[x.start:x.start + x.count]
+                rows.append(RowInput(r.slot, toks, x.start, [x.count - 1] if x.samples else [],
+                                     selective=bool(sch.selective and x.decode), sampling=r.sampling))
+            if self.record_timings:
+                # the first event is recorded when the host has filled the staging buffer, right before
+                # the step's first copy, so that the device time holds no wait for the host
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                runner.on_device_work = ev[0].record
+            logits, tokens = runner.step_and_sample(rows)
+            runner.on_device_work = None
+            if ev:
+                ev[1].record()
+            read = self._start_read(tokens)
+            if ev:
+                ev[2].record()      # after the copy to the host is asked for, before the host waits for it
+        if reuse is None or reuse == list(range(len(ahead["rows"]))):
+            self._run_ahead(plan, tokens)
+        new_tokens = self._finish_read(read)
+        if reuse is not None:
+            new_tokens = [new_tokens[i] for i in reuse]
         if ev:
-            ev[1].record()
-        new_tokens = self._to_host(tokens)
-        if ev:
-            ev[2].record()
             torch.cuda.synchronize()
             self.step_timings.append(dict(plan_ms=0.0, model_forward_ms=ev[0].elapsed_time(ev[1]),
                                           postprocess_ms=ev[1].elapsed_time(ev[2]),
                                           step_total_ms=(time.perf_counter() - t0) * 1e3,
-                                          active_bsz=len(rows), tokens=sum(x.count for x in plan),
+                                          active_bsz=len(plan), tokens=sum(x.count for x in plan),
                                           total_pages=sum(runner.cache.pages_in_use().values())))
         return sch.complete(plan, new_tokens)
 
-    def _to_host(self, tokens: torch.Tensor) -> List[int]:
-        """The device-to-host read of a step's result, through pinned memory."""
+    def _start_read(self, tokens: torch.Tensor):
+        """Starts the device-to-host read of a step's result, through pinned memory (two buffers
+        in turns: the read of the step that runs ahead is started before this one is finished)."""
         n = tokens.shape[0]
         if n == 0:
+            return None
+        self._read_turn ^= 1
+        buf = self._host_tokens[self._read_turn]
+        if buf is None or buf.numel() < n:
+            buf = self._host_tokens[self._read_turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+        buf[:n].copy_(tokens, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return buf, done, n
+
+    @staticmethod
+    def _finish_read(read) -> List[int]:
+        if read is None:
             return []
-        if self._host_tokens is None or self._host_tokens.numel() < n:
-            self._host_tokens = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
-        self._host_tokens[:n].copy_(tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._host_tokens[:n].tolist()
+        buf, done, n = read
+        done.synchronize()      # waits for this step only, not for the one launched after it
+        return buf[:n].tolist()
+
+    def _run_ahead(self, plan, tokens: torch.Tensor) -> None:
+        """Launches the next decode step before the host has read this one's tokens.
+
+        Only when the next step is certain but for stop tokens: every row of this step decodes one
+        token and cannot reach a length limit with it, nothing waits for admission, decode steps of
+        this size are replayed from a graph, and the pool has the pages.  The rows take their
+        tokens from this step's result on the device.  If the next plan turns out otherwise (a
+        request stopped, one was added), ``step`` drops what was launched here and runs the plan:
+        the launched step wrote keys and values only at positions the plan writes again, with the
+        same values."""
+        from ..cache.page_pool import OutOfPages
+        sch, runner = self.scheduler, self.runner
+        if not (self.run_ahead and self.cuda_graph_decode) or self.record_timings or sch.waiting or not plan:
+            return
+        if not runner.decode_graph_ready(len(plan)):
+            return
+        limit = runner.cache.max_seq_len
+        for x in plan:
+            r = x.request
+            if x.count != 1 or not x.samples or x.start + 1 < len(r.prompt):
+                return
+            after = x.start + 2          # tokens the request holds once this step's token is appended
+            if after >= min(r.max_length, limit):
+                return
+            if r.max_new_tokens is not None and len(r.output) + 1 >= r.max_new_tokens:
+                return
+        try:
+            for x in plan:
+                runner.cache.grow(x.request.slot, x.start + 2)
+        except OutOfPages:
+            return
+        rows = [RowInput(x.request.slot, [0], x.start + 1, [0], selective=bool(sch.selective), sampling=x.request.sampling)
+                for x in plan]
+        _, nxt = runner.step_and_sample(rows, tokens_from=tokens)
+        self._ahead = dict(rows=[(x.request.slot, x.start + 1) for x in plan], tokens=nxt, read=self._start_read(nxt))
+
+    @staticmethod
+    def _match_ahead(plan, ahead) -> Optional[List[int]]:
+        """For every row of the plan its place in the step that was launched ahead, when the plan
+        is that step or that step without some of its rows; else None."""
+        where = {key: i for i, key in enumerate(ahead["rows"])}
+        out = []
+        for x in plan:
+            i = where.get((x.request.slot, x.start))
+            if i is None or x.count != 1 or not x.samples or (out and i <= out[-1]):
+                return None
+            out.append(i)
+        return out
 
     def run_scheduler_loop(self) -> List[dict]:
         """Runs until every request is finished (or, in throughput mode, until the first one

@@ -98,6 +98,7 @@ class ModelRunner:
         self.err = ops.new_error_record(self.device)
         self._scratch: Dict[str, torch.Tensor] = {}
         self._staging = []      # ring of (pinned buffer, event)
+        self.on_device_work = None   # called once per step right before its first device operation (for timing)
         self._staging_next = 0
         self.plain_products = False
         self.plain_attention = False
@@ -217,6 +218,8 @@ class ModelRunner:
         self._fill(pinned.numpy(), layout, rows, q_lens, q_start, wants, max_pages)
         self.last_staging_bytes = size * 4
         dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        if self.on_device_work is not None:
+            self.on_device_work()
         dev.copy_(pinned[:size], non_blocking=True)
         self._staging[idx][1] = _record_event()
         return self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, max_seq)
@@ -245,16 +248,25 @@ class ModelRunner:
                        seeds=s["samp_seed"].view(torch.int64), positions=s["samp_pos"])
         return out
 
-    def step_and_sample(self, rows: List[RowInput]):
+    def decode_graph_ready(self, batch: int) -> bool:
+        """True when decode steps of this many rows are replayed from a captured graph already."""
+        g = self._graphs.get(batch)
+        return bool(self.cfg.cuda_graph_decode and g is not None and g["graph"] is not None)
+
+    def step_and_sample(self, rows: List[RowInput], tokens_from: Optional[torch.Tensor] = None):
         """One batch, and one new token for every wanted place (greedy, or as the row's
         ``sampling`` says).  Returns (logits, tokens), both on the device.  A step in which
         every row brings one token is replayed from a CUDA graph when the engine was set up
-        with ``cuda_graph_decode``."""
+        with ``cuda_graph_decode``.  ``tokens_from``: a device tensor with one token per row that
+        takes the place of the rows' own tokens (the tokens the step before sampled, which the
+        host has not read yet); only for steps that ``decode_graph_ready`` says are replayed."""
         if not rows:
             return (torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device),
                     torch.empty(0, dtype=torch.int32, device=self.device))
         if self.cfg.cuda_graph_decode and all(len(r.tokens) == 1 and list(r.want) == [0] for r in rows):
-            return self._graph_step(rows)
+            return self._graph_step(rows, tokens_from)
+        if tokens_from is not None:
+            raise ValueError("tokens from the device are taken by captured decode steps only")
         ctx = self.build_context(rows)
         logits = self.model.forward(ctx)
         tokens = self._sample(ctx, logits)
@@ -264,7 +276,7 @@ class ModelRunner:
         return logits, tokens
 
     # ---- decode steps from a CUDA graph ---------------------------------------------
-    def _graph_step(self, rows: List[RowInput]):
+    def _graph_step(self, rows: List[RowInput], tokens_from: Optional[torch.Tensor] = None):
         """Replays the captured decode step for this batch size.  All metadata lives in one
         device buffer of fixed layout that a single copy refreshes before the replay; block
         tables have their full width, the attention grid is the one sized for the longest
@@ -285,8 +297,15 @@ class ModelRunner:
         idx, pinned = self._pinned(size)
         self._fill(pinned.numpy(), layout, rows, q_lens, q_start, wants, max_pages)
         self.last_staging_bytes = size * 4
+        if self.on_device_work is not None:
+            self.on_device_work()
         dev.copy_(pinned[:size], non_blocking=True)
         self._staging[idx][1] = _record_event()
+        if tokens_from is not None:
+            if g["graph"] is None:
+                raise ValueError("tokens from the device are taken by captured decode steps only")
+            a, _ = layout["tokens"]
+            dev[a:a + B].copy_(tokens_from[:B])      # device to device, in stream order before the replay
 
         def run():
             ctx = self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, self.cache.max_seq_len)

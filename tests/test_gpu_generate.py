@@ -146,3 +146,46 @@ def test_cuda_graph_decode_gives_the_same_tokens(model_folders, selective):
     assert outs[True] == outs[False]
     if not selective:
         assert outs[True][1] == plain_greedy(plain, prompts[1], 31)
+
+
+@pytest.mark.parametrize("selective", [False, True])
+def test_decode_steps_launched_ahead_give_the_same_tokens(model_folders, selective):
+    """With CUDA-graph decode the engine launches step N + 1 before the host has read the tokens
+    of step N (they are taken on the device).  Requests that stop at a stop token, at their
+    length and at different steps, a request added while others decode, temperature sampling and
+    DELTA: the tokens are those of the engine that feeds every token back through the host."""
+    from delta_b200.engine import LMBackend
+    folder = model_folders["B"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(n, plain.cfg.vocab, 90 + i) for i, n in enumerate([30, 9, 50, 17])]
+    late = helpers.random_tokens(21, plain.cfg.vocab, 99)
+    # a stop token that the second request really meets: taken from a run without stop tokens
+    probe = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=False)
+    probe.load_model(folder)
+    probe.setup_caches(max_batch_size=1, max_seq_length=128, page_size=8)
+    stop = probe.generate([prompts[1]], 20)[0][12]
+    outs, launched = {}, {}
+    for ahead in (False, True):
+        e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=True)
+        e.run_ahead = ahead
+        e.load_model(folder)
+        e.setup_caches(max_batch_size=5, max_seq_length=128, page_size=8, check_kernel_errors=True,
+                       enable_selective_cache=selective, full_cache_layers=[1], subset_cache_size=4, L=2)
+        reused = 0
+        first = len(e.scheduler.requests)
+        e.add_requests(prompts[:1], [60], [], temperature=0.8, seed=5)
+        e.add_requests(prompts[1:2], [70], [stop])
+        e.add_requests(prompts[2:], [90, 128], [])
+        steps = 0
+        while e.scheduler.has_work():
+            had = e._ahead is not None
+            e.step()
+            reused += int(had)
+            steps += 1
+            if steps == 25:
+                e.add_requests([late], [64], [], temperature=0.5, seed=3)
+        outs[ahead] = [r.output for r in e.scheduler.requests[first:]]
+        launched[ahead] = reused
+    assert outs[True] == outs[False]
+    assert outs[True][1][-1] == stop and len(outs[True][1]) <= 13
+    assert launched[False] == 0 and launched[True] > 40
