@@ -76,7 +76,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   const int ks_begin = rank * per;
   const int ks_end = min(k_steps_total, ks_begin + per);
   const int n_steps = max(0, ks_end - ks_begin);
-
   const uint32_t full0 = s2u(&bars[0]), empty0 = s2u(&bars[16]), tfull = s2u(&bars[32]);
   if (tid == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -165,22 +164,62 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   tc_fence_before();
   if (splits > 1) cluster.sync(); else __syncthreads();
 
-  // block r of the cluster finishes rows [r * share, (r + 1) * share) of the tile
-  const int share = rows_out / splits;
+  // Block r of the cluster finishes rows [r * share, (r + 1) * share) of the tile, eight output
+  // columns of one token at a time: the partial sums of all blocks are asked for together (two
+  // 16-byte loads from each block's shared memory), added in rank order, and stored with 16 bytes.
+  const int share = rows_out / splits;          // a multiple of 8
   const int r_begin = rank * share;
-  for (int idx = tid; idx < share * a.M; idx += TC_THREADS) {
-    const int m = idx / share, r = r_begin + idx % share;
-    float g = 0.f, u = 0.f;
-    for (int b = 0; b < splits; ++b) {
-      const float* src = splits > 1 ? cluster.map_shared_rank(part, b) : part;
-      g += src[(size_t)m * TILE_ROWS + r];
-      if (a.swiglu) u += src[(size_t)m * TILE_ROWS + 64 + r];
+  const int groups = share / 8;
+  const float* parts[8];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) parts[b] = (b < splits && splits > 1) ? cluster.map_shared_rank(part, b) : part;
+  for (int item = tid; item < groups * a.M; item += TC_THREADS) {
+    const int m = item / groups, r = r_begin + (item % groups) * 8;
+    float4 g0[8], g1[8], u0[8], u1[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b < splits) {
+        const float* src = parts[b] + (size_t)m * TILE_ROWS + r;
+        g0[b] = *reinterpret_cast<const float4*>(src);
+        g1[b] = *reinterpret_cast<const float4*>(src + 4);
+        if (a.swiglu) {
+          u0[b] = *reinterpret_cast<const float4*>(src + 64);
+          u1[b] = *reinterpret_cast<const float4*>(src + 68);
+        }
+      }
+    }
+    float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      if (b < splits) {
+        y[0] += g0[b].x; y[1] += g0[b].y; y[2] += g0[b].z; y[3] += g0[b].w;
+        y[4] += g1[b].x; y[5] += g1[b].y; y[6] += g1[b].z; y[7] += g1[b].w;
+        if (a.swiglu) {
+          u[0] += u0[b].x; u[1] += u0[b].y; u[2] += u0[b].z; u[3] += u0[b].w;
+          u[4] += u1[b].x; u[5] += u1[b].y; u[6] += u1[b].z; u[7] += u1[b].w;
+        }
+      }
     }
     const int n = n0 + r;
-    if (good && n < (a.swiglu ? a.n_up : a.N)) {
-      const float y = a.swiglu ? g / (1.f + expf(-g)) * u : g;
-      if (a.out_f32) ((float*)a.out)[(size_t)m * a.ldc + n] = y;
-      else ((__nv_bfloat16*)a.out)[(size_t)m * a.ldc + n] = __float2bfloat16_rn(y);
+    if (good && n < (a.swiglu ? a.n_up : a.N)) {     // N and the first up row are multiples of 8: a group is in or out as a whole
+      if (a.swiglu) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = y[i] / (1.f + expf(-y[i])) * u[i];
+      }
+      if (a.out_f32) {
+        float* dst = (float*)a.out + (size_t)m * a.ldc + n;
+        *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
+      } else {
+        uint4 st;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]),
+                       p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
+        st.x = *reinterpret_cast<uint32_t*>(&p0);
+        st.y = *reinterpret_cast<uint32_t*>(&p1);
+        st.z = *reinterpret_cast<uint32_t*>(&p2);
+        st.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + (size_t)m * a.ldc + n) = st;
+      }
     }
   }
   if (splits > 1) cluster.sync(); else __syncthreads();   // nobody leaves while its memory is still read
@@ -212,6 +251,8 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   DK_REQUIRE((lda % 8) == 0 && (ldw % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0,
              "gemm_tc: operands must start on 16-byte boundaries with leading sizes that are multiples of 8");
   DK_REQUIRE(out_dtype == DK_BF16 || out_dtype == DK_F32, "gemm_tc: unknown output dtype %d", out_dtype);
+  DK_REQUIRE((ldc % 8) == 0 && ((uintptr_t)out % 16) == 0,
+             "gemm_tc: the output must start on a 16-byte boundary with a leading size that is a multiple of 8");
   TcArgs a;
   a.out = out;
   a.err = err;
