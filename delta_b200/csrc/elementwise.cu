@@ -158,7 +158,9 @@ extern "C" int dk_rms_norm(void* x, const void* add, const void* w, void* out, c
   if (n_rows == 0) return 0;
   DK_REQUIRE(n_rows > 0 && d > 0, "rms_norm: bad sizes rows=%d d=%d", n_rows, d);
   DK_REQUIRE(d <= 12000, "rms_norm: width %d is above the 12000 this kernel keeps in shared memory", d);
-  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  // few rows (a decode step): many threads per row shorten the one pass every block makes; many rows
+  // (a prompt): two vectors per thread and more blocks per SM carry more bytes (measured, width 4096)
+  const int threads = d >= 2048 ? ((n_rows >= 256 && d >= 4096) ? 256 : 512) : (d >= 512 ? 256 : 128);
   const size_t smem = (size_t)(d + 33) * sizeof(float);
   const int vec = dtype == DK_BF16 ? 8 : 4;
   const bool use_vec = (d % vec) == 0 && d / vec <= 2 * threads;
@@ -192,19 +194,51 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
+// The same with 16-byte loads and stores, for I a multiple of the vector length: blockIdx.y walks
+// the tokens, the threads of blockIdx.x the vectors of a token, so no index is divided.
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int T_) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int nvec = I / VEC;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= nvec) return;
+  for (int t = blockIdx.y; t < T_; t += gridDim.y) {
+    const uint4* row = reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I);
+    const uint4 g4 = row[v], u4 = row[nvec + v];
+    const T* ge = reinterpret_cast<const T*>(&g4);
+    const T* ue = reinterpret_cast<const T*>(&u4);
+    uint4 o4;
+    T* oe = reinterpret_cast<T*>(&o4);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float g = to_f32<T>(ge[e]);
+      oe[e] = from_f32<T>(g / (1.f + expf(-g)) * to_f32<T>(ue[e]));
+    }
+    reinterpret_cast<uint4*>(out + (size_t)t * I)[v] = o4;
+  }
+}
+
 extern "C" int dk_silu_mul(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
   if (T_ == 0) return 0;
   DK_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);
-  const size_t total = (size_t)T_ * I;
+  DK_REQUIRE(dtype == DK_F32 || dtype == DK_BF16, "silu_mul: unknown dtype %d", dtype);
+  const int vec = dtype == DK_BF16 ? 8 : 4;
   const int threads = 256;
+  if ((I % vec) == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    dim3 grid((I / vec + threads - 1) / threads, T_ < 32768 ? T_ : 32768);
+    if (dtype == DK_F32)
+      silu_mul_vec_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I, T_);
+    else
+      silu_mul_vec_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, T_);
+    return dk_check_launch("silu_mul");
+  }
+  const size_t total = (size_t)T_ * I;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == DK_F32)
     silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
-  else if (dtype == DK_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
   else
-    DK_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
+    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
   return dk_check_launch("silu_mul");
 }
 

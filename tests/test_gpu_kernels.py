@@ -77,12 +77,14 @@ def test_rms_norm(dtype, wdtype, d):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_silu_mul(dtype):
+@pytest.mark.parametrize("T, I", [(9, 344), (5, 345), (300, 11008), (1, 8)])
+def test_silu_mul(dtype, T, I):
+    """Widths that take the 16-byte path and one that does not; more rows than one pass of the grid."""
     o = ops()
-    gu = (torch.randn(9, 2 * 344, device=DEV) * 3).to(dtype)
-    out = torch.empty(9, 344, dtype=dtype, device=DEV)
+    gu = (torch.randn(T, 2 * I, device=DEV) * 3).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
     o.silu_mul(gu, out)
-    g, u = gu[:, :344].float(), gu[:, 344:].float()
+    g, u = gu[:, :I].float(), gu[:, I:].float()
     assert torch.allclose(out.float(), (torch.nn.functional.silu(g) * u).to(dtype).float(), **tol(dtype))
 
 
