@@ -84,10 +84,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
                                                                           const DkAttnParams p) {
   using L = Layout<HD>;
   constexpr int STAGES = L::STAGES;
-  const int row = blockIdx.z, h = blockIdx.y;
+  // Blocks are handed out with x fastest: all heads of the latest query tile first (it has the most
+  // keys), then all heads of the tile before, and so on, so that the long blocks start first and
+  // the short ones fill the gaps; heads that share keys and values run side by side.
+  const int row = blockIdx.z, h = blockIdx.x;
   const int q_len = p.row_q_len[row];
   if (p.row_filter == 2 && q_len == 1) return;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // late tiles have the most keys: start them first
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int q0 = qt * QT;
   if (q0 >= q_len) return;
 
@@ -359,7 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       const bool two = n_tiles > 1;                     // O_1 holds nothing when there was one tile
       constexpr int OC = HD / 64;                       // chunks of 32 columns this thread writes
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)(t0 + r) * p.H + h) * HD + w * (HD / 2);
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < OC; ++c) {
         float o0[32], o1[32];
         const uint32_t col = (uint32_t)(w * (HD / 2) + c * 32);
@@ -416,7 +419,7 @@ int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
     }
     configured = true;
   }
-  dim3 grid((max_q_len + QT - 1) / QT, p.H, p.rows);
+  dim3 grid(p.H, (max_q_len + QT - 1) / QT, p.rows);
   attention_prefill_tc_kernel<HD><<<grid, THREADS, L::TOTAL, stream>>>(map_q, map_kv, map_run, p);
   return dk_check_launch("attention_prefill_tc");
 }
@@ -440,7 +443,7 @@ extern "C" int dk_attention_prefill_tc(const DkAttnParams* pp, int max_q_len, cu
   DK_REQUIRE(max_q_len >= 1, "attention_prefill_tc: max_q_len must be positive");
   DK_REQUIRE(p.scale > 0.f, "attention_prefill_tc: the scale of the scores must be positive");
   DK_REQUIRE(p.row_q_start && p.row_q_len && p.row_pos_start && p.block_table, "attention_prefill_tc: row tables are missing");
-  DK_REQUIRE(p.H <= 65535 && p.rows <= 65535, "attention_prefill_tc: grid too large");
+  DK_REQUIRE((max_q_len + QT - 1) / QT <= 65535 && p.rows <= 65535, "attention_prefill_tc: grid too large");
   DK_REQUIRE(((uintptr_t)p.q % 16) == 0 && ((uintptr_t)p.kv % 16) == 0 && ((uintptr_t)p.out % 16) == 0,
              "attention_prefill_tc: queries, cache and output must start on 16-byte boundaries");
   return p.hd == 64 ? launch<64>(p, max_q_len, stream) : launch<128>(p, max_q_len, stream);
