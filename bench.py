@@ -16,7 +16,10 @@ step.  It prints ONE JSON line:
              pinned host memory and reads the new tokens back to the host.  ``value`` is the
              engine as it runs by default: a decode step is launched while the host still reads
              the step before, with its tokens taken from that step's result on the device;
-             ``value_tokens_fed_back_through_host`` is the same with that switched off
+             ``value_tokens_fed_back_through_host`` is the same with that switched off.
+             (Run ahead, the loop can come out a little faster than ``value``: the steps of
+             ``value`` are timed one by one, each starting on an idle GPU with its copies on the
+             critical path, while here the next step's copies queue behind the running step.)
   prefill    one prompt of 2,048 tokens in one step; frac = flops / time / peak
   roofline   bytes a decode step has to read (every weight once, and the cache of the
              live requests) / its time, against the copy bandwidth
