@@ -1,6 +1,7 @@
 """Configurations with awkward sizes through the whole engine, in both precisions: head sizes in
 steps of 16 (including 80, 112 and 256), numbers of heads and groups that are odd or prime, widths
-and vocabularies that are no multiple of 8, one layer and five layers."""
+and vocabularies that are no multiple of 8, one layer and five layers, a window with the head size of the
+tensor-core kernels."""
 import pytest
 import torch
 
@@ -20,6 +21,11 @@ ODD = {
                   intermediate_size=64, vocab_size=301, rope_theta=10000.0, rms_norm_eps=1e-5, max_position_embeddings=256),
     "hd64g9": dict(BASE, hidden_size=144, num_hidden_layers=5, num_attention_heads=18, num_key_value_heads=2, head_dim=64,
                    intermediate_size=112, vocab_size=777, rope_theta=5000000.0, rms_norm_eps=1e-5, max_position_embeddings=256),
+    # head size 64 with a window in every second layer: the tensor-core attention kernels mask by window,
+    # and the windowed group gives pages back while the requests run
+    "hd64win": dict(BASE, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                    intermediate_size=144, vocab_size=600, rope_theta=1000000.0, rms_norm_eps=1e-5, max_position_embeddings=256,
+                    sliding_window=40, layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]),
     "hd128g3": dict(BASE, hidden_size=160, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
                     intermediate_size=208, vocab_size=1000, rope_theta=5000000.0, rms_norm_eps=1e-5, max_position_embeddings=256),
 }
