@@ -14,12 +14,22 @@
 // The kernel is bound by the bytes of K and V it has to read once; the tensor-core
 // work is small beside it, which is why the legacy warp-level MMA is enough here.
 //
+// TMA variant (pages of 8 tokens or more, no score dump): a tile whose pages follow one another
+// in the pool and are wholly visible to the query is fetched by one thread with one TMA box per
+// half of the head and K/V (a 4-D view of the cache: a run of pages of one head) instead of 16
+// cp.async per thread with their address arithmetic, which is a third of the loop's
+// instructions.  Tiles at a window's or the request's edge, scattered pages and chosen pages
+// keep the cp.async path with its groups; a TMA tile is waited for on its stage's mbarrier.  The shared-memory layout
+// of this variant is the one TMA's 128-byte swizzle leaves: halves of the head side by side,
+// rows of 128 bytes, 16-byte chunks exchanged by the row's number.
+//
 // It takes: the whole cache, a window of it, or the list of chosen pages of DELTA's
 // subset layers; and it can dump the scaled scores and the log-sum-exp for DELTA's
 // page scoring (reference: backend.py:191-221, 562-577).
 #include "common.cuh"
 #include "attention_params.h"
 #include "mma_helpers.cuh"
+#include "tcgen05_helpers.cuh"
 
 namespace {
 constexpr int TILE = 64;     // keys per tile
@@ -78,19 +88,32 @@ __device__ __forceinline__ void mma_rows(float* c, float (&zd)[2], const uint32_
   }
 }
 
-template <int HD, bool LOW>
-__global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkAttnParams p) {
+// Byte offset of 16-byte chunk ``chunk`` of key ``tok`` inside a K or V tile.
+template <int HD, bool TMA>
+__device__ __forceinline__ uint32_t tile_offset(int tok, int chunk) {
+  if constexpr (TMA) return (uint32_t)((chunk >> 3) * (TILE * 128) + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4));
+  else return (uint32_t)(tok * (HD * 2) + ((chunk ^ (tok & 7)) * 16));
+}
+
+template <int HD, bool LOW, bool TMA>
+__global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __grid_constant__ CUtensorMap map_run,
+                                                                       const DkAttnParams p) {
   constexpr int R = LOW ? 1 : 2;              // rows of the tile a thread keeps (g, and g + 8)
   constexpr int CHUNKS = HD / 8;              // 16-byte chunks per key row
   constexpr int ROW_BYTES = HD * 2;
   constexpr int TILE_BYTES = TILE * ROW_BYTES;  // one of K or V
   constexpr int KB = HD / 16;                 // k-blocks of the QK product
   constexpr int NT = HD / 8;                  // n-tiles of the PV product
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the TMA variant needs its tiles on a 1024-byte boundary (the swizzle pattern repeats every 1024 bytes)
+  unsigned char* smem = TMA ? reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
   unsigned char* kv_smem = smem;                                  // STAGES * 2 * TILE_BYTES
   int* s_key = reinterpret_cast<int*>(smem + STAGES * 2 * TILE_BYTES);  // STAGES * TILE key positions (-1: no key)
   int* s_lp = s_key + STAGES * TILE;     // logical page of each of this block's entries
   int* s_page = s_lp + p.block_entries;       // its physical page, -1: none (p.block_entries = entries a block can have)
+  int* s_run = s_page + p.block_entries;      // TMA: first physical page of a tile that is one visible run of pages, else -1
+  __shared__ __align__(8) unsigned long long full_bar[STAGES];   // TMA: a stage's tile has arrived
+  __shared__ int s_timeout;                                       // TMA: a wait for a tile gave up
 
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
@@ -130,7 +153,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     s_lp[i] = lp;
     s_page[i] = page;
   }
+  if (TMA && tid == 0) {
+    s_timeout = 0;
+    for (int s = 0; s < STAGES; ++s) mbar_init(s2u(&full_bar[s]), 1);   // the one thread that asks for the boxes arrives
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
   __syncthreads();
+  if (TMA) {
+    // which tiles are one run of wholly visible pages
+    for (int tile = tid; tile < n_tiles; tile += NTHREADS) {
+      const int el0 = tile * pages_per_tile;
+      int first = (el0 + pages_per_tile <= e_end - e_begin) ? s_page[el0] : -1;
+      for (int k = 0; k < pages_per_tile && first >= 0; ++k) {
+        const int lp = s_lp[el0 + k];
+        // (the page this launch appends to is fetched the ordinary way: it was just written with ordinary stores)
+        if (s_page[el0 + k] != first + k || lp * ps < ri.lo || lp * ps + ps - 1 > ri.pos || (p.fuse == 2 && lp == ri.pos / ps))
+          first = -1;
+      }
+      s_run[tile] = first;
+    }
+    __syncthreads();
+  }
 
   // Fused append: the block whose share ends with the request's newest page rotates the new
   // token's key, writes key and value to that page, and only then starts to read pages.
@@ -206,7 +249,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     ld_tok[i] = tok;
     ld_pg[i] = tok / ps;
     ld_src[i] = (tok % ps) * HD + part * 8;                       // elements inside the (page, K, head) block
-    ld_dst[i] = tok * ROW_BYTES + ((part ^ (tok & 7)) * 16);      // bytes inside a K or V tile
+    ld_dst[i] = (int)tile_offset<HD, TMA>(tok, part);             // bytes inside a K or V tile
   }
   const size_t page_stride = (size_t)2 * p.KV * ps * HD;           // elements from one page to the next
   const size_t v_offset = (size_t)p.KV * ps * HD;                  // from a page's K to its V
@@ -217,6 +260,21 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     const uint32_t kdst = smem_u32(kv_smem + (size_t)stage * 2 * TILE_BYTES);
     const uint32_t vdst = kdst + TILE_BYTES;
     const int el0 = tile * pages_per_tile;
+    if constexpr (TMA) {
+      const int first = s_run[tile];
+      if (first >= 0) {       // the same answer in every thread
+        if (tid == 0) {
+          const uint32_t bar = s2u(&full_bar[stage]);
+          mbar_expect_tx(bar, 2u * TILE_BYTES);
+#pragma unroll
+          for (int half = 0; half < HD / 64; ++half) {
+            tma_load_4d(kdst + half * (TILE * 128), &map_run, half * 64, 0, kvh, first, bar);
+            tma_load_4d(vdst + half * (TILE * 128), &map_run, half * 64, 0, p.KV + kvh, first, bar);
+          }
+        }
+        return true;
+      }
+    }
     bool all_valid = true;
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {
@@ -255,7 +313,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
   }
   const float sc_log2 = p.scale * 1.4426950408889634f;
 
-#pragma unroll
   // full[s]: every key of the tile in stage s is one the query may see, so its scores need no
   // masking.  Each thread knows it for its own chunks; the barriers below collect the votes.
   unsigned full = 0;   // bit s: stage s
@@ -267,14 +324,26 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
     if (__syncthreads_and(mine)) full |= 1u << s;
   }
   bool issued_ok = true;
+  unsigned tma_parity = 0;   // bit s: parity of the next TMA tile of stage s
   for (int tile = 0; tile < n_tiles; ++tile) {
-    cp_async_wait<STAGES - 2>();
+    cp_async_wait<STAGES - 2>();      // tiles fetched by cp.async (a tile fetched by TMA leaves an empty group)
+    if constexpr (TMA) {
+      if (s_run[tile] >= 0) {           // fetched by TMA: its stage's barrier tells; the parity of a stage flips with each such tile
+        const int st = tile % STAGES;
+        if (!mbar_wait(s2u(&full_bar[st]), (tma_parity >> st) & 1u)) s_timeout = 1;
+        tma_parity ^= 1u << st;
+      }
+    }
     {
       // the barrier also tells whether the tile issued in the iteration before is wholly visible
       const bool prev = __syncthreads_and(issued_ok) != 0;
       if (tile > 0) {
         const unsigned bit = 1u << ((tile - 1 + STAGES - 1) % STAGES);
         full = prev ? (full | bit) : (full & ~bit);
+      }
+      if (TMA && s_timeout) {      // somebody's wait ran out (written before the barrier above): nothing is stored
+        if (tid == 0) dk_report(p.err, DK_DEV_TIMEOUT, row, kvh, split);
+        return;
       }
       const int nxt = tile + STAGES - 1;
       issued_ok = true;
@@ -300,7 +369,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
       for (int kb = 0; kb < KB; kb += 2) {
         const int chunk = 2 * kb + (lane >> 3);
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, kbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
+        ldmatrix_x4(b0, b1, b2, b3, kbase + tile_offset<HD, TMA>(tok, chunk));
         mma_rows<LOW>(s[j], zd, qa[kb], b0, b1);
         mma_rows<LOW>(s[j], zd, qa[kb + 1], b2, b3);
       }
@@ -374,7 +443,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const DkA
       for (int n = 0; n < NT; n += 2) {
         const int chunk = n + (lane >> 4);
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tok * ROW_BYTES + ((chunk ^ (tok & 7)) * 16));
+        ldmatrix_x4_trans(b0, b1, b2, b3, vbase + tile_offset<HD, TMA>(tok, chunk));
         mma_rows<LOW>(o[n], zd, pa, b0, b1);
         mma_rows<LOW>(o[n + 1], zd, pa, b2, b3);
       }
@@ -463,7 +532,7 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
 }
 
-template <int HD, bool LOW>
+template <int HD, bool LOW, bool TMA>
 int launch(const DkAttnParams& pin, cudaStream_t stream) {
   DkAttnParams p = pin;
   // entries (pages) one block can be given: the widest request split evenly
@@ -472,12 +541,23 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     dk_set_error("attention_decode: %d pages per block are above the 8192 it keeps in shared memory; use more splits", p.block_entries);
     return DK_ERR_ARG;
   }
-  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)2 * p.block_entries * sizeof(int);
+  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)3 * p.block_entries * sizeof(int);
   constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
-  const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+  const size_t smem = (tile_bytes > merge_bytes ? tile_bytes : merge_bytes) + (TMA ? 1024 : 0);
+  CUtensorMap map_run;
+  memset(&map_run, 0, sizeof(map_run));
+  if (TMA) {
+    // the cache as [page][K|V, head][offset][hd]: a run of pages of one head in one box of a tile's pages
+    const unsigned long long dims[4] = {(unsigned long long)HD, (unsigned long long)p.ps, (unsigned long long)(2 * p.KV),
+                                        (unsigned long long)p.num_pages};
+    const unsigned long long strides[3] = {(unsigned long long)HD * 2, (unsigned long long)p.ps * HD * 2,
+                                           (unsigned long long)2 * p.KV * p.ps * HD * 2};
+    DK_REQUIRE(make_tensor_map_bf16_4d(&map_run, p.kv, dims, strides, p.ps, TILE / p.ps),
+               "attention_decode: cannot encode the tensor map of runs of pages");
+  }
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
       return DK_ERR_LAUNCH;
@@ -485,7 +565,7 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     configured = smem;
   }
   dim3 grid(p.splits, p.KV, p.rows);
-  attention_decode_kernel<HD, LOW><<<grid, NTHREADS, smem, stream>>>(p);
+  attention_decode_kernel<HD, LOW, TMA><<<grid, NTHREADS, smem, stream>>>(map_run, p);
   int rc = dk_check_launch("attention_decode");
   if (rc != 0 || p.splits == 1) return rc;
   dim3 mgrid(p.H, p.rows);
@@ -528,8 +608,17 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
   DK_REQUIRE(p.sel_pages == nullptr || (p.sel_count != nullptr && p.row_flags != nullptr && p.row_slot != nullptr),
              "attention_decode: chosen pages are given without their counts, row flags or slots");
   const bool low = p.H / p.KV <= 8;
-  if (p.hd == 64) return low ? launch<64, true>(p, stream) : launch<64, false>(p, stream);
-  return low ? launch<128, true>(p, stream) : launch<128, false>(p, stream);
+  // the TMA variant: pages of at least 8 tokens (a page is a multiple of the swizzle's 8 rows), no score
+  // dump (a dump needs every key's position), a cache that starts on a 16-byte boundary
+  // and a caller that has not said (reserved bit 0) that its pages lie scattered: then no tile is a run,
+  // and the cp.async path of the TMA variant is the slower one (measured: 122 against 111 us)
+  const bool tma = p.ps >= 8 && p.dump == nullptr && ((uintptr_t)p.kv % 16) == 0 && (p.reserved & 1) == 0;
+  if (p.hd == 64) {
+    if (tma) return low ? launch<64, true, true>(p, stream) : launch<64, false, true>(p, stream);
+    return low ? launch<64, true, false>(p, stream) : launch<64, false, false>(p, stream);
+  }
+  if (tma) return low ? launch<128, true, true>(p, stream) : launch<128, false, true>(p, stream);
+  return low ? launch<128, true, false>(p, stream) : launch<128, false, false>(p, stream);
 }
 
 // --------------------------------------------------------------------------------------

@@ -30,5 +30,5 @@ struct DkAttnParams {
   int fuse;                // decode kernel: q points into rows [q | k | v] that are not rotated yet; the kernel rotates
                            // q and k itself and (fuse == 2) appends k and v of the new token to its page
   int rope_positions;      // rows of rope_table
-  int reserved;
+  int reserved;            // bit 0 (decode kernel): the pages of the rows lie scattered over the pool, do not look for runs
 };

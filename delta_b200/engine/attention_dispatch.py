@@ -13,9 +13,13 @@ import torch
 
 from ..kernels import ops
 
+import os
+
+_NO_RUNS = os.environ.get("DELTA_B200_DECODE_NO_TMA") == "1"   # for measurements: never look for runs of pages
 SM_COUNT = 148
 DECODE_TILE = 64
 MAX_SPLITS = 64
+TMA_MIN_TILES = 16    # tiles a block must walk for the decode kernel's TMA variant to be taken
 BLOCKS_PER_SM = 2     # the decode kernel's registers and shared memory let two blocks share an SM
 
 
@@ -34,11 +38,31 @@ def can_fuse_rope_append(ctx, H: int, KV: int, hd: int, ps: int, interleaved: bo
             and ops.attention_decode_supported(ctx.dtype, H, KV, hd, ps))
 
 
+def _pages_scattered(ctx, params) -> bool:
+    """True when fewer than half of the rows' pages follow their predecessor in the pool: the decode
+    kernel then does not look for runs of pages to fetch with one copy."""
+    import numpy as np
+    for g in ctx.cache.groups.values():
+        if g.page_size != params.ps:
+            continue
+        slots = [r.slot for r in ctx.host["rows"]]
+        t = g.table[slots]
+        held = t[:, 1:] >= 0
+        n = int(held.sum())
+        return n > 0 and int(((t[:, 1:] - t[:, :-1] == 1) & held).sum()) * 2 < n
+    return False
+
+
 def _decode(ctx, params, row_filter: int) -> None:
     max_keys = ctx.max_seq_len if not params.window else min(ctx.max_seq_len, params.window + params.ps)
     splits = ctx.fixed_decode_splits or decode_splits(ctx.num_rows, params.KV, max_keys)
     params.splits = splits
     params.row_filter = row_filter
+    # The variant that fetches runs of pages by TMA pays for finding the runs at the start of a block:
+    # it wins when a block walks many tiles (batch 64 at 4,096 keys: 111 -> 85 us) and loses a little
+    # when it walks few (batch 8 at 4,096 keys with 9 splits, 7 tiles a block: +1.6 % on the step).
+    long_blocks = -(-max_keys // (DECODE_TILE * splits)) >= TMA_MIN_TILES
+    params.reserved = 0 if (long_blocks and not _NO_RUNS and not _pages_scattered(ctx, params)) else 1
     if splits > 1:
         n = ops.attention_decode_scratch_floats(ctx.num_rows, params.H, params.hd, splits)
         params.scratch = ctx.scratch("attention.decode_partials", (n,), torch.float32).data_ptr()

@@ -328,15 +328,26 @@ def make_far_key_stand_out(case, b, far, h):
     case.kv[page, 0, g, off] = case.k[b][far, g].to(DEV)
 
 
+@pytest.mark.parametrize("pages", ["scattered", "runs", "scattered, told so"])
 @pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (1, 3, 64, 8), (16, 1, 128, 64), (5, 2, 64, 32), (4, 2, 128, 16)])
-def test_attention_decode_against_plain(G, KV, hd, ps):
+def test_attention_decode_against_plain(G, KV, hd, ps, pages):
     """The split-key tensor-core kernel against the plain kernel and the float32 answer:
-    contexts from one key to hundreds, ends of pages, a far key that dominates."""
+    contexts from one key to hundreds, ends of pages, a far key that dominates.  With pages in
+    runs the kernel fetches whole tiles by TMA, with scattered pages by cp.async in the same
+    layout; told that the pages are scattered it runs its variant without TMA."""
     o = ops()
     H = G * KV
     dtype = torch.bfloat16
     seq_lens = [1, ps, ps + 1, 63, 64, 65, 400, 1000]
-    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, [1] * len(seq_lens), seed=G + hd)
+    case = PagedCase(dtype, H, KV, hd, ps, seq_lens, [1] * len(seq_lens), seed=G + hd, scatter=pages != "runs")
+    if pages == "scattered, told so":
+        inner = case.params
+
+        def told(out, **kw):
+            p = inner(out, **kw)
+            p.reserved = 1
+            return p
+        case.params = told
     make_far_key_stand_out(case, 7, 3, H - 1)        # among 1000 keys, the fourth one wins for the last head
     ref, ref_lse, _ = case.reference()
     assert ref[7].view(H, hd)[H - 1].sub(case.v[7][3, KV - 1].float()).abs().max() < 1e-3
