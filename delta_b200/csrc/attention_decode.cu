@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
 
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  if (TMA && tid == 0)   // the descriptor is on its way while the pages are looked up
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_run)) : "memory");
   const int G = p.H / p.KV, ps = p.ps;
   if (p.row_filter == 1 && p.row_q_len[row] != 1) return;   // a row of a prompt: the prefill kernel's
   const RowInfo ri = row_info(p, row);

@@ -9,17 +9,17 @@ every size.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
-
-import os
 
 _NO_RUNS = os.environ.get("DELTA_B200_DECODE_NO_TMA") == "1"   # for measurements: never look for runs of pages
 SM_COUNT = 148
 DECODE_TILE = 64
 MAX_SPLITS = 64
-TMA_MIN_TILES = 16    # tiles a block must walk for the decode kernel's TMA variant to be taken
+TMA_MIN_TILES = int(os.environ.get("DELTA_B200_TMA_MIN_TILES", "16"))    # tiles a block must walk for the decode kernel's TMA variant to be taken
 BLOCKS_PER_SM = 2     # the decode kernel's registers and shared memory let two blocks share an SM
 
 
