@@ -49,7 +49,7 @@ constexpr int THREADS = (MMA_WARP + 2) * 32;
 constexpr int BOX_BYTES = 128 * 128;   // 128 rows of one 128-byte swizzle row each
 constexpr float RESCALE_STEP = 8.f;    // in powers of two
 constexpr int TMEM_COLS = 512;
-constexpr int COL_S = 0, COL_O = 2 * KT;   // S_0, S_1 (P_w lies over the first 64 columns of S_w), then O_0, O_1
+constexpr int COL_S = 0, COL_O = 2 * KT;   // S_0, S_1, then O_0, O_1
 
 template <int HD>
 struct Layout {
