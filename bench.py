@@ -267,6 +267,9 @@ def main() -> int:
     print("kernels chosen per product (rows bucket, N, K, swiglu, out): " +
           "; ".join(f"{k[0]}x{k[1]}x{k[2]}{'sw' if k[3] else ''}->{v}" for k, v in sorted(linear.choices().items(), key=str)),
           file=sys.stderr)
+    print("measured in isolation, us:",
+          "; ".join(f"{k[0]}x{k[1]}x{k[2]}{'sw' if k[3] else ''}: " + " ".join(f"{c}={t:.1f}" for c, t in v.items())
+                    for k, v in sorted(linear.timings().items(), key=str)), file=sys.stderr)
     print(json.dumps(out))
     return 0
 
