@@ -58,6 +58,8 @@ _SIGNATURES = {
     "dk_gemm_small_m_supported": [I, I, I, I],
     "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "dk_gemm_tc_supported": [I, I, I, I],
+    "dk_gemm_stream_k_supported": [I, I, I, I],
+    "dk_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, I, P, P, P],
 }
 
 
@@ -76,6 +78,8 @@ def load():
         lib.dk_sizeof_attn_params.restype = I
         lib.dk_attention_decode_scratch_floats.restype = C.c_longlong
         lib.dk_attention_decode_scratch_floats.argtypes = [I, I, I, I]
+        lib.dk_gemm_stream_k_workspace_bytes.restype = C.c_longlong
+        lib.dk_gemm_stream_k_workspace_bytes.argtypes = [I]
         if lib.dk_sizeof_attn_params() != C.sizeof(AttnParams):
             raise KernelError(f"AttnParams is {C.sizeof(AttnParams)} bytes in Python and "
                               f"{lib.dk_sizeof_attn_params()} in the library: the two declarations differ")

@@ -260,6 +260,34 @@ def gemm_tc(x, w, out, swiglu=False, splits=1, err=None):
     return out
 
 
+def gemm_stream_k_supported(M, N, K, swiglu=False) -> bool:
+    return bool(_l.load().dk_gemm_stream_k_supported(M, N, K, int(swiglu)))
+
+
+_stream_k_workspace = {}
+
+
+def gemm_stream_k(x, w, out, swiglu=False, err=None):
+    """out = x @ w^T for up to 128 rows of bfloat16 x as one persistent tcgen05 kernel: the
+    (tile, K step) sequence is cut into one equal piece per SM, tiles that two pieces share are
+    summed through a workspace in block order.  The workspace (partials and flags, zero at first)
+    belongs to the device and is used by one stream at a time.
+    ``swiglu``: w holds gate rows then up rows, out [M, N/2] = silu(x gate^T) * (x up^T)."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_stream_k: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} or dtypes do not fit")
+    ws = _stream_k_workspace.get(x.device)
+    if ws is None:
+        ws = torch.zeros(int(_l.load().dk_gemm_stream_k_workspace_bytes(128)), dtype=torch.uint8, device=x.device)
+        _stream_k_workspace[x.device] = ws
+    _l.check(_l.load().dk_gemm_stream_k(_ptr(x, "x"), _ptr(w, "w"), _ptr(out, "out"), M, N, K, x.stride(0), w.stride(0),
+                                        out.stride(0), dtype_code(out.dtype), int(swiglu), _ptr(ws, "workspace", torch.uint8),
+                                        _ptr(err, "err", torch.int32), _stream()), "gemm_stream_k")
+    return out
+
+
 def recent_pages(row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, ps, ratio):
     i32 = torch.int32
     _l.check(_l.load().dk_recent_pages(_ptr(row_slot, "row_slot", i32), _ptr(row_flags, "row_flags", i32),

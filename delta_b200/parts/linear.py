@@ -5,10 +5,11 @@ reduced-precision matrix mode, no split over K).  bfloat16 activations go
 through the tensor cores.  For large batches (prompt portions) that is the
 library product the reference uses for its ``nn.Linear`` layers
 (DELTA/Engine/DELTA/model.py:369-370, 498-500).  For the few rows of a decode
-step the product is a stream over the weights and three kernels compete: the
-tcgen05/TMA kernel (with 1, 2, 4 or 8 blocks sharing K as a cluster), the
-warp-level MMA kernel that loads weights straight into fragments, and the
-library.  Which one is fastest depends on the shape, so each (rows bucket, N, K,
+step the product is a stream over the weights and four kernels compete: the
+warp-level MMA kernel that loads weights straight into fragments, the persistent
+tcgen05/TMA kernel that cuts the (tile, K step) sequence into one piece per SM,
+the tcgen05/TMA kernel with one block per tile (1, 2, 4 or 8 blocks sharing K as
+a cluster), and the library.  Which one is fastest depends on the shape, so each (rows bucket, N, K,
 epilogue) is measured once on the real weights, with the L2 flushed between runs,
 and the winner is kept.
 """
@@ -47,12 +48,16 @@ def _candidates(m: int, n: int, k: int, swiglu: bool, out_dtype) -> List[str]:
                 c.append(f"tc{s}")
     if out_dtype == torch.bfloat16:
         c.append("lib")
+    if ops.gemm_stream_k_supported(m, n, k, swiglu):
+        c.append("sk")       # last: a tie in isolation goes to the kernels that end sooner on most SMs
     return c
 
 
 def _run(kind: str, x, w, out, swiglu: bool, err=None):
     if kind == "small":
         return ops.gemm_small_m(x, w, out, swiglu=swiglu)
+    if kind == "sk":
+        return ops.gemm_stream_k(x, w, out, swiglu=swiglu, err=err)
     if kind.startswith("tc"):
         return ops.gemm_tc(x, w, out, swiglu=swiglu, splits=int(kind[2:]), err=err)
     ops.count_launch()

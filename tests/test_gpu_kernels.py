@@ -214,6 +214,50 @@ def test_gemm_tc_swiglu(M, I, K, splits):
     assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 100, 128])
+@pytest.mark.parametrize("N, K", [(128, 64), (1000, 344), (4096, 4096), (1408, 11008), (2048, 520), (20000, 256)])
+def test_gemm_stream_k(M, N, K):
+    """The persistent tcgen05 product: the (tile, K step) sequence in one equal piece per SM.  One
+    piece for the whole product; tiles shared by three and by six blocks; pieces of many whole
+    tiles with a shared tile at either end; sizes that end inside a tile, a box and a step.  The
+    second and third launch use the same workspace (flags carry the launch's number) and give the
+    same bits."""
+    o = ops()
+    torch.manual_seed(M * 5 + N)
+    err = o.new_error_record(DEV)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_stream_k(x, w, out, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2)
+    out32 = torch.full((M, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_stream_k(x, w, out32, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(out32, ref, atol=1e-3, rtol=1e-4)
+    again = torch.full((M, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_stream_k(x, w, again, err=err)
+    o.raise_if_error(err)
+    assert torch.equal(again, out32)
+
+
+@pytest.mark.parametrize("M", [3, 64])
+@pytest.mark.parametrize("I, K", [(64, 128), (704, 344), (11008, 4096)])
+def test_gemm_stream_k_swiglu(M, I, K):
+    o = ops()
+    torch.manual_seed(M + I)
+    err = o.new_error_record(DEV)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    want = torch.nn.functional.silu(ref[:, :I]) * ref[:, I:]
+    act = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_stream_k(x, w, act, swiglu=True, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
+
+
 def test_gemm_small_m_refuses_what_it_does_not_take():
     o = ops()
     assert not o.gemm_small_m_supported(65, 64, 64)
