@@ -665,3 +665,34 @@ def test_temperature_and_top_p():
     freq = torch.bincount(out.long().cpu(), minlength=16)[:4].float() / 4000
     want = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)
     assert (freq - want).abs().max() < 0.03
+
+
+def test_product_tuner_keeps_the_preferred_kernel_within_the_margin(monkeypatch):
+    """The tuner's rule with made-up times: a later candidate replaces an earlier one only when it
+    is faster by more than the margin; every candidate it names really runs and gives the product."""
+    from delta_b200.parts import linear
+    o = ops()
+    err = o.new_error_record(DEV)
+    M, N, K = 16, 512, 256
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    cands = linear._candidates(M, N, K, False, torch.bfloat16)
+    assert cands[0] == "small" and cands[-1] == "sk" and "lib" in cands and "tc1" in cands
+    ref = x.float() @ w.float().T
+    for kind in cands:
+        out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+        linear._run(kind, x, w, out, False, err)
+        o.raise_if_error(err)
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2), kind
+
+    def tuned(times):
+        order = iter(times)
+        monkeypatch.setattr(linear, "_time", lambda fn, reps=12: next(order))
+        return linear._tune(M, x, w, False, torch.bfloat16, err)
+
+    n = len(cands)
+    assert tuned([10.0] * n) == cands[0]
+    assert tuned([10.0] + [10.0 * (1 - linear.MARGIN) + 0.01] * (n - 1)) == cands[0]      # not enough
+    assert tuned([10.0, 9.0] + [10.0] * (n - 2)) == cands[1]                               # 10 % faster
+    assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.5]) == cands[1]                       # 5.6 % on the second: stays
+    assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.0]) == cands[-1]
