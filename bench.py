@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the delta_b200 engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--shape yi-6b|yi-9b|yi-34b]
 
 Default run: the layer sizes of Yi-6B (32 layers, hidden 4096, 32 heads over 4
 key-value heads of 128, intermediate 11008, vocabulary 64000), random bfloat16
@@ -47,7 +47,13 @@ YI_6B = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_size
              num_attention_heads=32, num_key_value_heads=4, intermediate_size=11008, vocab_size=64000,
              rope_theta=5000000.0, rms_norm_eps=1e-5, max_position_embeddings=4096, hidden_act="silu",
              tie_word_embeddings=False, torch_dtype="bfloat16")
-FULL_LAYERS = 32
+# other shapes of the same architecture, for runs beside the default one (--shape)
+SHAPES = {
+    "yi-6b": ("Yi-6B shape", YI_6B),
+    "yi-9b": ("Yi-1.5-9B shape", dict(YI_6B, num_hidden_layers=48, rms_norm_eps=1e-6)),
+    "yi-34b": ("Yi-34B shape", dict(YI_6B, hidden_size=7168, num_hidden_layers=60, num_attention_heads=56,
+                                    num_key_value_heads=8, intermediate_size=20480)),
+}
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
 
 
@@ -132,7 +138,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers go into config)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="yi-6b")
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
@@ -155,7 +162,11 @@ def main() -> int:
     from delta_b200.engine import LMBackend
     from delta_b200.kernels import ops
 
-    cfg = dict(YI_6B, num_hidden_layers=args.layers)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    full_layers = shape_cfg["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(shape_cfg, num_hidden_layers=args.layers)
     pk = peaks()
     weight_bytes, kv_per_tok, prefill_flops = model_numbers(cfg, args.layers)
     ctx_len = args.context
@@ -246,10 +257,10 @@ def main() -> int:
             points[f"decode_b{b}"] = b / (d_ms / 1e3)
 
     out = {
-        "metric": "decode tok/s (Yi-6B shape, bf16, batch 8, context 4096)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "metric": f"decode tok/s ({shape_name}, bf16, batch {args.batch}, context {ctx_len})", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
-        "config": {"model": "Yi-6B shape", "layers": args.layers, "layers_of_named_config": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": args.layers, "layers_of_named_config": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": args.batch, "seq_len": ctx_len, "page_size": 16, "parallelism": "single GPU",
