@@ -51,12 +51,17 @@ class CacheGroup:
         self.page_size = page_size
         self.pool = PagePool(num_pages, shuffle_seed)
         self.index_of = {cid: i for i, cid in enumerate(self.cache_ids)}
-        self.kv = torch.zeros((len(self.cache_ids), num_pages, 2, spec.kv_heads, page_size, spec.head_dim),
+        # one page more than the pool hands out: the spare page that the padding slot points at
+        self.kv = torch.zeros((len(self.cache_ids), num_pages + 1, 2, spec.kv_heads, page_size, spec.head_dim),
                               dtype=dtype, device=device)
+        self.spare_page = num_pages
         # host block tables; -1 = no page.  first_page[slot]: pages below it were given back.
-        self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
-        self.first_page = np.zeros(max_slots, dtype=np.int64)
-        self.num_logical = np.zeros(max_slots, dtype=np.int64)  # logical pages ever reached
+        # Row max_slots is the padding slot: one logical page, the spare one, for ever.
+        self.table = np.full((max_slots + 1, max_pages_per_request), -1, dtype=np.int32)
+        self.first_page = np.zeros(max_slots + 1, dtype=np.int64)
+        self.num_logical = np.zeros(max_slots + 1, dtype=np.int64)  # logical pages ever reached
+        self.table[max_slots, 0] = self.spare_page
+        self.num_logical[max_slots] = 1
 
     def pages_needed(self, slot: int, new_len: int) -> int:
         want = (new_len + self.page_size - 1) // self.page_size
@@ -69,7 +74,13 @@ class CacheGroup:
 
 class CacheManager:
     """Owns every cache group and every state slot.  ``device`` may be "cpu" for tests of
-    the bookkeeping; kernels only ever see CUDA tensors."""
+    the bookkeeping; kernels only ever see CUDA tensors.
+
+    Beside the ``max_slots`` slots that requests get there is one padding slot
+    (``padding_slot``), which no request ever holds: it has a row in every block table
+    with one page, a spare page outside the pool, and a row in every state.  A decode step
+    captured for a rounded-up batch size points its spare rows at it (position 0), so that
+    they read and write nothing that belongs to a request."""
 
     def __init__(self, cache_specs: Dict[int, CacheSpec], state_specs: Dict[str, StateSpec], *, max_slots: int,
                  max_seq_len: int, page_size: int, num_pages, dtype=torch.bfloat16, device="cuda", shuffle_seed=None):
@@ -90,7 +101,8 @@ class CacheManager:
                 self.group_of_cache[cid] = g
         self.state_specs = dict(state_specs)
         self.states: Dict[str, torch.Tensor] = {
-            k: torch.full((self.max_slots, *s.shape), s.fill, dtype=s.dtype, device=device) for k, s in state_specs.items()}
+            k: torch.full((self.max_slots + 1, *s.shape), s.fill, dtype=s.dtype, device=device) for k, s in state_specs.items()}
+        self.padding_slot = self.max_slots
         self.seq_len = np.zeros(self.max_slots, dtype=np.int64)
         self._free_slots = list(range(self.max_slots - 1, -1, -1))
         self._live = [False] * self.max_slots

@@ -248,9 +248,22 @@ class ModelRunner:
                        seeds=s["samp_seed"].view(torch.int64), positions=s["samp_pos"])
         return out
 
+    def graph_batch(self, batch: int) -> int:
+        """The batch size a decode step of ``batch`` rows is captured for: up to 8 as it is, above
+        that the next of 12, 16, 24, 32, 48, 64, 96, ... (at most half as many rows again), never
+        above the engine's largest batch.  So a batch that shrinks request by request, as the end
+        of a wave of requests does, replays a dozen graphs instead of meeting a new size, with its
+        eager runs and its capture, at every step."""
+        if batch <= 8:
+            return batch
+        size = 8
+        while size < batch:
+            size = size * 3 // 2 if (size & (size - 1)) == 0 else size * 4 // 3
+        return max(batch, min(size, self.cfg.max_batch))
+
     def decode_graph_ready(self, batch: int) -> bool:
         """True when decode steps of this many rows are replayed from a captured graph already."""
-        g = self._graphs.get(batch)
+        g = self._graphs.get(self.graph_batch(batch))
         return bool(self.cfg.cuda_graph_decode and g is not None and g["graph"] is not None)
 
     def step_and_sample(self, rows: List[RowInput], tokens_from: Optional[torch.Tensor] = None):
@@ -284,8 +297,13 @@ class ModelRunner:
         Reference: backend.py:974-1001 (when a graph is used), 1119-1162 (two warm-up runs,
         then capture)."""
         from .attention_dispatch import decode_splits
-        B = len(rows)
-        q_lens, q_start, wants, max_seq = self._check_rows(rows)
+        n_real = len(rows)
+        self._check_rows(rows)
+        # The step is captured for a rounded-up batch size; the spare rows decode position 0 of
+        # the cache's padding slot, which belongs to no request, and their tokens are dropped.
+        B = self.graph_batch(n_real)
+        rows = list(rows) + [RowInput(self.cache.padding_slot, [0], 0, [0])] * (B - n_real)
+        q_lens, q_start, wants = [1] * B, list(range(B)), list(range(B))
         max_pages = self.cache.max_pages_per_request
         g = self._graphs.get(B)
         if g is None:
@@ -305,7 +323,7 @@ class ModelRunner:
             if g["graph"] is None:
                 raise ValueError("tokens from the device are taken by captured decode steps only")
             a, _ = layout["tokens"]
-            dev[a:a + B].copy_(tokens_from[:B])      # device to device, in stream order before the replay
+            dev[a:a + n_real].copy_(tokens_from[:n_real])      # device to device, in stream order before the replay
 
         def run():
             ctx = self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, self.cache.max_seq_len)
@@ -320,9 +338,9 @@ class ModelRunner:
         if g["graph"] is None:
             if g["warm"] < 2:           # eager runs first: they size every scratch buffer
                 g["warm"] += 1
-                out = run()
+                logits, tokens = run()
                 self.steps_run += 1
-                return out
+                return logits[:n_real], tokens[:n_real]
             # the eager runs have sized the scratch buffers; now record the same launches
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -339,7 +357,8 @@ class ModelRunner:
         self.graph_replays += 1
         if self.cfg.check_kernel_errors:
             ops.raise_if_error(self.err)
-        return g["out"]
+        logits, tokens = g["out"]
+        return logits[:n_real], tokens[:n_real]
 
     # ---- convenience used by replay and tests --------------------------------------
     def run_rows(self, rows: List[RowInput]) -> torch.Tensor:

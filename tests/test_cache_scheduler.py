@@ -62,7 +62,7 @@ def test_layers_share_a_group_and_windows_have_their_own():
     m = manager(window=6)
     assert set(m.groups) == {"kv2x8", "kv2x8w6"}
     assert m.groups["kv2x8"].cache_ids == [0, 1] and m.groups["kv2x8w6"].cache_ids == [2]
-    assert m.layer_kv(1).shape == (16, 2, 2, 4, 8)
+    assert m.layer_kv(1).shape == (16 + 1, 2, 2, 4, 8)      # the pool's 16 pages and the padding slot's spare page
     s = m.acquire_slot()
     for n in range(1, 41):
         m.grow(s, n)
@@ -79,10 +79,24 @@ def test_layers_share_a_group_and_windows_have_their_own():
     assert m.pages_in_use() == {"kv2x8": 0, "kv2x8w6": 0}
 
 
+def test_the_padding_slot_holds_the_spare_page_and_no_pool_page():
+    m = manager(num_pages=16, page_size=4, max_slots=4)
+    slots = [m.acquire_slot() for _ in range(4)]
+    assert m.padding_slot not in slots and m.free_slots == 0
+    for g in m.groups.values():
+        assert g.table[m.padding_slot, 0] == g.spare_page == 16 and (g.table[m.padding_slot, 1:] == -1).all()
+        assert g.pool.free_pages == 16          # the spare page is not one of the pool's
+    tables = m.block_tables_for([slots[0], m.padding_slot])
+    assert all(int(t[1, 0]) == 16 for t in tables.values())
+    m.check()
+
+
 def test_state_slots_are_reset_at_admission():
     m = manager(states={"toy": StateSpec((3,), torch.float32, 0.5), "count": StateSpec((), torch.int32, -1)})
     s = m.acquire_slot()
-    assert m.states["toy"].shape == (4, 3) and m.states["count"].shape == (4,)
+    # a row for each of the four slots and one for the padding slot, which is never handed out
+    assert m.states["toy"].shape == (4 + 1, 3) and m.states["count"].shape == (4 + 1,)
+    assert m.padding_slot == 4 and m.free_slots == 3
     m.states["toy"][s] = 9.0
     m.states["count"][s] = 4
     m.release_slot(s)

@@ -189,3 +189,34 @@ def test_decode_steps_launched_ahead_give_the_same_tokens(model_folders, selecti
     assert outs[True] == outs[False]
     assert outs[True][1][-1] == stop and len(outs[True][1]) <= 13
     assert launched[False] == 0 and launched[True] > 40
+
+
+@pytest.mark.parametrize("selective", [False, True])
+def test_rounded_up_decode_batches_give_the_same_tokens(model_folders, selective):
+    """Above 8 rows a captured decode step has a rounded-up batch size (12, 16, ...); its spare
+    rows decode position 0 of the cache's padding slot.  Thirteen requests that end one after the
+    other, so that the batch passes 13, 12, 11, ... rows: the tokens are those of the engine
+    without CUDA graphs, and no page is lost."""
+    from delta_b200.engine import LMBackend
+    folder = model_folders["B"]
+    plain = PlainYi(folder)
+    prompts = [helpers.random_tokens(5 + 3 * i, plain.cfg.vocab, 300 + i) for i in range(13)]
+    lengths = [len(p) + 6 + 2 * i for i, p in enumerate(prompts)]
+    outs, sizes = {}, {}
+    for graph in (False, True):
+        e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=graph)
+        e.load_model(folder)
+        e.setup_caches(max_batch_size=13, max_seq_length=96, page_size=8, check_kernel_errors=True,
+                       enable_selective_cache=selective, full_cache_layers=[1], subset_cache_size=4, L=2)
+        first = len(e.scheduler.requests)
+        e.add_requests(prompts, lengths, [])
+        while e.scheduler.has_work():
+            e.step()
+        outs[graph] = [r.output for r in e.scheduler.requests[first:]]
+        sizes[graph] = sorted(e.runner._graphs)
+        e.runner.cache.check()
+        assert all(v == 0 for v in e.runner.cache.pages_in_use().values())
+    assert outs[True] == outs[False]
+    assert [len(o) for o in outs[True]] == [6 + 2 * i for i in range(13)]
+    assert sizes[True] == [1, 2, 3, 4, 5, 6, 7, 8, 12, 13] and sizes[False] == []
+    assert e.runner.graph_batch(9) == 12 and e.runner.graph_batch(13) == 13 and e.runner.graph_batch(8) == 8

@@ -309,7 +309,7 @@ def test_toy_parts_are_registered_built_and_stepped(tmp_path):
         refs = [toy_plain(folder, t) for t in toks]
         r = ModelRunner(folder, engine_config=EngineConfig(max_batch=4, max_seq_len=64, page_size=8, num_pages=40, dtype="float32"))
         assert set(r.cache.groups) == {"kv1x16"} and r.cache.groups["kv1x16"].cache_ids == [0, 2]
-        assert r.cache.states["toy.1.mean.state"].shape == (4, 48)
+        assert r.cache.states["toy.1.mean.state"].shape == (4 + 1, 48)     # four requests and the padding slot
         prompt_lens = [n // 2 for n in lengths]
         mixed, ends = helpers.mixed(lengths, prompt_lens, seed=2)
         for what, steps, e in (("whole", helpers.whole(lengths), None), ("one by one", helpers.last_one_by_one(lengths), None),
