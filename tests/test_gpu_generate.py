@@ -220,3 +220,32 @@ def test_rounded_up_decode_batches_give_the_same_tokens(model_folders, selective
     assert [len(o) for o in outs[True]] == [6 + 2 * i for i in range(13)]
     assert sizes[True] == [1, 2, 3, 4, 5, 6, 7, 8, 12, 13] and sizes[False] == []
     assert e.runner.graph_batch(9) == 12 and e.runner.graph_batch(13) == 13 and e.runner.graph_batch(8) == 8
+
+
+def test_waves_of_requests_repeat_their_outputs(model_folders):
+    """Three waves of 20 to 40 requests drawn from 12 prompts, more than the engine's 20 slots, so
+    that requests wait, batches grow and shrink through the graph sizes 1..8, 12, 16, 20 and
+    pages are used again: in 32-bit a prompt gives the same tokens wherever it runs, and the
+    cache is empty after every wave."""
+    import random
+    from delta_b200.engine import LMBackend
+    folder = model_folders["A"]
+    vocab = PlainYi(folder).cfg.vocab
+    rng = random.Random(3)
+    base = [helpers.random_tokens(rng.randrange(3, 60), vocab, 400 + i) for i in range(12)]
+    e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=True)
+    e.load_model(folder)
+    e.setup_caches(max_batch_size=20, max_seq_length=128, page_size=16, max_tokens_per_step=96, check_kernel_errors=True)
+    seen = {}
+    for wave in range(3):
+        idx = [rng.randrange(12) for _ in range(rng.randrange(20, 41))]
+        first = len(e.scheduler.requests)
+        e.add_requests([base[i] for i in idx], [len(base[i]) + 10 + 5 * (i % 5) for i in idx], [])
+        while e.scheduler.has_work():
+            e.step()
+        for i, r in zip(idx, e.scheduler.requests[first:]):
+            assert len(r.output) == 10 + 5 * (i % 5), r.finish_reason
+            assert seen.setdefault(i, r.output) == r.output, f"wave {wave}: prompt {i} gave other tokens than before"
+        e.runner.cache.check()
+        assert all(v == 0 for v in e.runner.cache.pages_in_use().values())
+    assert set(e.runner._graphs) >= {8, 12, 16, 20}
