@@ -518,15 +518,37 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   if (p.row_filter == 1 && p.row_q_len[row] != 1) return;
   const float* sc = reinterpret_cast<const float*>(p.scratch);
   const int t = p.row_q_start[row] + p.row_q_len[row] - 1;
-  float M = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, sc[part_ml_index(p, row, h, s)]);
-  float L = 0.f, acc = 0.f;
-  if (M != -INFINITY) {
-    for (int s = 0; s < p.splits; ++s) {
-      const float ms = sc[part_ml_index(p, row, h, s)];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += sc[part_ml_index(p, row, h, s) + 1] * f;
-      if (d < HD) acc += sc[part_o_index(p, row, h, s, HD) + d] * f;
+  // Sixteen splits at a time: their maxima, sums and outputs are asked for together (one round
+  // trip to the L2 instead of one per split), then added in split order; a later group rescales
+  // what the groups before it added.
+  constexpr int GROUP = 16;
+  const float* ml = sc + part_ml_index(p, row, h, 0);          // {m, l} of split s at ml[2 s]
+  const float* po = sc + part_o_index(p, row, h, 0, HD) + (d < HD ? d : 0);   // this thread's output of split s at po[s HD]
+  float M = -INFINITY, L = 0.f, acc = 0.f;
+  for (int s0 = 0; s0 < p.splits; s0 += GROUP) {
+    float m[GROUP], l[GROUP], o[GROUP];
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      const int s = s0 + j;
+      const bool ok = s < p.splits;
+      m[j] = ok ? ml[2 * s] : -INFINITY;
+      l[j] = ok ? ml[2 * s + 1] : 0.f;
+      o[j] = ok ? po[(size_t)s * HD] : 0.f;
+    }
+    float group_max = M;
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) group_max = fmaxf(group_max, m[j]);
+    if (group_max != -INFINITY) {
+      const float keep = M == -INFINITY ? 0.f : exp2f(M - group_max);
+      L *= keep;
+      acc *= keep;
+#pragma unroll
+      for (int j = 0; j < GROUP; ++j) {
+        const float f = m[j] == -INFINITY ? 0.f : exp2f(m[j] - group_max);
+        L += l[j] * f;
+        acc += o[j] * f;
+      }
+      M = group_max;
     }
   }
   if (d < HD)
