@@ -245,3 +245,17 @@ def test_random_load_finishes_everything(seed):
         if r.status == FINISHED:
             assert r.total_len >= min(r.max_length, 48) or r.finish_reason != "length"
     assert all(v == 0 for v in m.pages_in_use().values()) and m.free_slots == 3
+
+
+def test_decode_graph_sizes_round_up_by_at_most_a_half():
+    """Batch sizes of captured decode steps: exact up to 8, then 12, 16, 24, 32, 48, 64, ..., capped
+    by the engine's largest batch."""
+    from types import SimpleNamespace
+    from delta_b200.engine.step import ModelRunner
+    size = lambda b, most: ModelRunner.graph_batch(SimpleNamespace(cfg=SimpleNamespace(max_batch=most)), b)
+    assert [size(b, 256) for b in range(1, 9)] == list(range(1, 9))
+    assert [size(b, 256) for b in (9, 12, 13, 16, 17, 25, 33, 49, 64, 65, 97, 129, 200)] == \
+        [12, 12, 16, 16, 24, 32, 48, 64, 64, 96, 128, 192, 256]
+    for b in range(1, 257):
+        assert b <= size(b, 256) <= max(8, b * 3 // 2) and size(size(b, 256), 256) == size(b, 256)
+    assert size(13, 13) == 13 and size(9, 10) == 10 and size(60, 70) == 64 and size(66, 70) == 70
