@@ -131,6 +131,38 @@ def model_numbers(cfg: dict, layers: int):
     return weight_bytes, kv_bytes_per_token, prefill_flops
 
 
+def reference_arm(args) -> int:
+    """The unmodified reference on the same decode workload: ``baseline/reference_arm.py`` in a
+    process of its own (nothing of delta_b200 is imported there); its JSON line is printed as it
+    is.  Whatever goes wrong becomes the ``unavailable`` line with the reason."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:400]}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("the reference arm is set up for one GPU")
+    script = ROOT / "baseline" / "reference_arm.py"
+    if not (ROOT / "baseline" / "_ref" / "DELTA").is_dir():
+        return unavailable("no copy of hoenza/DELTA under baseline/_ref (it has no setup.py or pyproject.toml, so pip "
+                           "cannot install it; a plain copy of the tree is what its own scripts use)")
+    if args.shape == "yi-9b":
+        return unavailable("the reference's table of models has no 48-layer Yi entry (DELTA/Engine/DELTA/model.py:72-97)")
+    cmd = [sys.executable, str(script), "--batch", str(args.batch), "--context", str(args.context), "--steps", str(args.steps),
+           "--warmup", str(max(3, args.warmup)), "--shape", args.shape]
+    if args.no_graph:
+        cmd.append("--no-graph")
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    except subprocess.TimeoutExpired:
+        return unavailable("the reference did not finish within 1500 s")
+    sys.stderr.write(r.stderr[-4000:])
+    for line in reversed(r.stdout.splitlines()):
+        if line.startswith('{"impl"'):
+            print(line)
+            return 0
+    tail = (r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["no output"])[-1]
+    return unavailable(f"the reference ended with code {r.returncode}: {tail}")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -148,10 +180,7 @@ def main() -> int:
     ap.add_argument("--subset_cache_size", type=int, default=64)
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "hoenza/DELTA has no setup.py or pyproject.toml (pip: 'not installable'), and its attention "
-                          "library pins kernels that have no sm_100 build"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported (single-GPU engine tier)")
         return 2
