@@ -8,8 +8,8 @@ layer, DELTA/Engine/DELTA/model.py:99-127), ``PageManager`` and
 pages (backend.py:263, page_selector_v2.py:62-63).
 
 What differs, on purpose:
-  * Layers are sorted into groups by what they keep per token (key-value heads,
-    head size, window).  A group has a pool and block tables of its own; all layers
+  * Layers are sorted into groups by what they keep per token (the layout of a
+    page, which the mixer declares, and the window).  A group has a pool and block tables of its own; all layers
     of a group share a request's page ids.  A group with a window gives pages back
     as soon as the window has passed them; the others when the request ends.
   * A request holds ceil(len / page_size) pages: no empty page in advance
@@ -17,8 +17,10 @@ What differs, on purpose:
     scheduler.py:60-66).
   * Growing a request is all or nothing over the groups; ``OutOfPages`` leaves
     everything as it was, and the scheduler decides what happens then.
-  * Layout of a layer's cache: [page][K|V][kv head][offset][head_dim], so that the
-    keys of one (page, head) are one contiguous tile.
+  * What a page holds is the mixer's business: the manager allocates
+    [layers of the group][page][*layout] from the layout the mixer declares.  The
+    attention part keeps [K|V][kv head][offset][head_dim], so that the keys of one
+    (page, head) are one contiguous tile.
 """
 from __future__ import annotations
 
@@ -36,7 +38,7 @@ from .page_pool import OutOfPages, PagePool
 class LayerCacheView:
     """What a mixer gets for one run: its layer's pages and the block table of its group
     for the rows of this step."""
-    kv: torch.Tensor            # [num_pages, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor         # [num_pages, *page layout]: the pages of this layer
     block_table: torch.Tensor   # [rows, max_pages] int32 (device), -1 where no page is held
     page_size: int
     writes: bool
@@ -52,8 +54,7 @@ class CacheGroup:
         self.pool = PagePool(num_pages, shuffle_seed)
         self.index_of = {cid: i for i, cid in enumerate(self.cache_ids)}
         # one page more than the pool hands out: the spare page that the padding slot points at
-        self.kv = torch.zeros((len(self.cache_ids), num_pages + 1, 2, spec.kv_heads, page_size, spec.head_dim),
-                              dtype=dtype, device=device)
+        self.pages = torch.zeros((len(self.cache_ids), num_pages + 1, *spec.page_shape(page_size)), dtype=dtype, device=device)
         self.spare_page = num_pages
         # host block tables; -1 = no page.  first_page[slot]: pages below it were given back.
         # Row max_slots is the padding slot: one logical page, the spare one, for ever.
@@ -93,7 +94,7 @@ class CacheManager:
         self.groups: Dict[str, CacheGroup] = {}
         self.group_of_cache: Dict[int, CacheGroup] = {}
         for spec, cids in by_spec.items():
-            name = f"kv{spec.kv_heads}x{spec.head_dim}" + (f"w{spec.window}" if spec.window else "")
+            name = spec.describe()
             n = num_pages[name] if isinstance(num_pages, dict) else int(num_pages)
             g = CacheGroup(name, spec, cids, n, page_size, self.max_slots, self.max_pages_per_request, dtype, device, shuffle_seed)
             self.groups[name] = g
@@ -197,9 +198,9 @@ class CacheManager:
         return {n: g.table[slots] if len(slots) else np.zeros((0, self.max_pages_per_request), np.int32)
                 for n, g in self.groups.items()}
 
-    def layer_kv(self, cache_id: int) -> torch.Tensor:
+    def layer_pages(self, cache_id: int) -> torch.Tensor:
         g = self.group_of_cache[cache_id]
-        return g.kv[g.index_of[cache_id]]
+        return g.pages[g.index_of[cache_id]]
 
     def check(self) -> None:
         """Bookkeeping invariants: every held page belongs to exactly one live request."""

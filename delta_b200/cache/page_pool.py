@@ -24,6 +24,7 @@ class PagePool:
             raise ValueError("a page pool needs at least one page")
         self.num_pages = int(num_pages)
         order = list(range(self.num_pages - 1, -1, -1))  # page 0 is handed out first
+        self.shuffled = shuffle_seed is not None            # pages of a request lie scattered over the pool
         if shuffle_seed is not None:
             random.Random(shuffle_seed).shuffle(order)
         self._free: List[int] = order

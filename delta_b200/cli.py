@@ -10,7 +10,11 @@ tests/reasoni.py:70-121; the reasoning datasets are not part of this engine),
 model folder (config.json and safetensors) instead of a converted ``model.pth``.
 Added: ``--random_weights SEED`` with ``--config`` for a model without a folder,
 ``--prompt_len``, ``--max_new_tokens``, ``--temperature``, ``--top_p``, ``--dtype``,
-``--page_size``, ``--max_tokens_per_step``, ``--throughput_mode``, ``--out``.
+``--page_size``, ``--max_tokens_per_step``, ``--throughput_mode``, ``--out``,
+``--step_timings`` (time every step with CUDA events, as the reference always does, and
+write ``logs/step_timings_<time>.json``; without it the loop never waits for the device
+except to read tokens, and launches decode steps ahead of the host), ``--tuning_file``
+(save and reuse the measured choice of product kernels).
 
 Example:
     python -m delta_b200.cli --model /models/Yi-1.5-6B --B 64 --max_len 4096 \\
@@ -31,24 +35,24 @@ def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="delta_b200", description="Generate with the delta_b200 engine.")
     p.add_argument("--model", type=Path, default=None, help="model folder (config.json + safetensors)")
     p.add_argument("--model_name", type=str, default=None, help="name or folder of the tokenizer (optional)")
-    p.add_argument("--B", type=int, default=16, help="Batch size.")
-    p.add_argument("--max_len", type=int, default=2048, help="Maximum generation length")
-    p.add_argument("--seed", type=int, default=123, help="Random seed.")
+    p.add_argument("--B", type=int, default=16, help="request slots: the most requests that run at a time")
+    p.add_argument("--max_len", type=int, default=2048, help="most tokens a request may reach, prompt included (a multiple of 128)")
+    p.add_argument("--seed", type=int, default=123, help="seed of the prompts and of temperature sampling")
     p.add_argument("--cuda_graph_decode", action="store_true",
-                   help="Use CUDA Graph replay for steady one-token decode.")
-    p.add_argument("--printoutput", action="store_true", help="Whether to print sample outputs.")
+                   help="replay steps in which every request decodes one token from a recorded CUDA graph")
+    p.add_argument("--printoutput", action="store_true", help="print what the first requests generated")
     p.add_argument("--dataset", type=str, choices=["dummy1tok", "dummy4tok", "random"], default="dummy4tok",
                    help="synthetic prompts: one or four copies of one token, or random ids of --prompt_len")
-    p.add_argument("--num_samples", type=int, default=16, help="Number of samples to evaluate")
-    p.add_argument("--dummy_token_id", type=int, default=None, help="Token id of the dummy prompts (default: bos or 1).")
+    p.add_argument("--num_samples", type=int, default=16, help="how many requests are made")
+    p.add_argument("--dummy_token_id", type=int, default=None, help="the token the dummy prompts repeat (default: bos_token_id, else 1)")
     p.add_argument("--full_cache_layers", nargs="+", type=int, default=None,
-                   help="Layer indices that use full KV cache (e.g., --full_cache_layers 1 2 10 20)")
+                   help="indices of the layers that read every page; a full layer followed by another kind chooses the pages")
     p.add_argument("--subset_cache_ratio", type=float, default=0.5, help="accepted and unused, as in the reference")
     p.add_argument("--compression_ratio", type=float, default=1.0,
-                   help="Minimum full/subset page ratio required before DELTA switches to subset decode")
-    p.add_argument("--subset_cache_size", type=int, default=1024, help="Pages a subset layer reads per request")
-    p.add_argument("--L", type=int, default=8, help="The last L pages always kept.")
-    p.add_argument("--enable_selective_cache", action="store_true", help="Enable selective KV cache optimization")
+                   help="a request reads a subset once its pages / min(pages, subset_cache_size) exceed this")
+    p.add_argument("--subset_cache_size", type=int, default=1024, help="pages per request that the other layers read")
+    p.add_argument("--L", type=int, default=8, help="the newest L pages are always among the chosen")
+    p.add_argument("--enable_selective_cache", action="store_true", help="DELTA on: layers outside --full_cache_layers read chosen pages")
     # added
     p.add_argument("--random_weights", type=int, default=None, metavar="SEED", help="random weights instead of a folder's")
     p.add_argument("--config", type=Path, default=None, help="config.json for --random_weights")
@@ -62,6 +66,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max_tokens_per_step", type=int, default=2048)
     p.add_argument("--throughput_mode", action="store_true", help="stop when the first request finishes")
     p.add_argument("--out", type=Path, default=None, help="write the result JSON here")
+    p.add_argument("--step_timings", action="store_true",
+                   help="time every step (collect_pages, plan, model_forward, postprocess, step_total) and write logs/step_timings_<time>.json")
+    p.add_argument("--tuning_file", type=Path, default=None,
+                   help="JSON file with the measured choice of product kernels: read if it exists, written at the end")
     return p
 
 
@@ -76,6 +84,9 @@ def main(argv=None) -> int:
     random.seed(args.seed)
 
     from .engine import LMBackend
+    from .parts import linear
+    if args.tuning_file is not None and args.tuning_file.is_file():
+        linear.load_choices(args.tuning_file)
     eng = LMBackend(dtype=args.dtype, device="cuda:0", cuda_graph_decode=args.cuda_graph_decode)
     if args.random_weights is not None:
         cfg_path = args.config or (args.model / "config.json" if args.model else None)
@@ -91,7 +102,7 @@ def main(argv=None) -> int:
                      full_cache_layers=args.full_cache_layers, subset_cache_size=args.subset_cache_size,
                      compression_ratio=args.compression_ratio, L=args.L)
     eng.throughput_mode = args.throughput_mode
-    eng.record_timings = True
+    eng.record_timings = bool(args.step_timings)
     tok = None
     if args.model_name:
         from transformers import AutoTokenizer   # the tokenizer only; no model code of that package is used
@@ -119,7 +130,14 @@ def main(argv=None) -> int:
     summary = dict(total_time_s=total, requests=len(results), prompt_tokens=st["prompt_tokens"],
                    generated_tokens=st["generated_tokens"], tokens_per_second=st["generated_tokens"] / total if total else 0.0,
                    steps=st["steps"], preemptions=st["preemptions"],
+                   graph_captures=eng.runner.graph_captures, graph_replays=eng.runner.graph_replays,
+                   graph_fallbacks=dict(eng.runner.graph_fallbacks),
                    decode_step_ms_mean=(sum(s["model_forward_ms"] for s in decode) / len(decode)) if decode else None)
+    if args.step_timings:
+        path = eng.save_step_timings("logs", meta=dict(args={k: str(v) for k, v in vars(args).items()}))
+        summary["step_timings_file"] = str(path) if path else None
+    if args.tuning_file is not None:
+        linear.save_choices(args.tuning_file)
     print(json.dumps(summary))
     if args.printoutput:
         for r in results[:4]:

@@ -1,57 +1,15 @@
-"""Engine options: cache sizing, precision, DELTA's selective cache.
+"""Engine options: cache sizing, precision, limits of a step.
 
 The reference passes these as keyword arguments of ``LMBackend``
-(DELTA/Engine/DELTA/backend.py:29-48) and as attributes put on
-``model.config`` by its scripts (tests/reasoni.py:327-335).  The names of the
-selective-cache options are the reference's command-line names
-(tests/reasoni.py:251-262).
+(DELTA/Engine/DELTA/backend.py:29-48) and ``setup_caches`` (backend.py:247-256).
+What belongs to one architecture (DELTA's selective cache, the pairing of rotary
+positions) is not known here: it travels in ``options`` to the function that
+builds that architecture's model specification.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Optional
-
-
-@dataclass(frozen=True)
-class SelectiveCacheConfig:
-    """DELTA: which layers read the whole cache and how many pages the others read.
-
-    ``full_cache_layers`` are layer indices (tests/reasoni.py:251).  A full
-    layer followed by a non-full layer scores the pages and chooses
-    ``subset_cache_size`` of them for the layers after it
-    (DELTA/Engine/DELTA/model.py:177-194).  The last ``L`` pages are always
-    chosen (page_selector_v2.py:120-123); ``L`` is clamped to
-    ``subset_cache_size``.  A request uses the subset once
-    pages / min(pages, subset_cache_size) > ``compression_ratio``
-    (backend.py:1893-1897, decided per request here, per batch there).
-    """
-    full_cache_layers: tuple = ()
-    subset_cache_size: int = 1024
-    compression_ratio: float = 1.0
-    L: int = 8
-    position_bias: float = 1e-7
-
-    def __post_init__(self):
-        object.__setattr__(self, "full_cache_layers", tuple(sorted(set(int(i) for i in self.full_cache_layers))))
-        if self.subset_cache_size < 1:
-            raise ValueError("subset_cache_size must be at least 1")
-        if self.L < 1:
-            raise ValueError("L must be at least 1: the page that holds the newest token is always read")
-        if self.compression_ratio < 1.0:
-            raise ValueError("compression_ratio must be at least 1")
-
-    @property
-    def keep_last(self) -> int:
-        return min(self.L, self.subset_cache_size)
-
-    def role(self, layer: int, num_layers: int) -> str:
-        """'full', 'planner' (full, and it chooses pages for what follows) or 'subset'."""
-        if not self.full_cache_layers:
-            return "full"
-        if layer in self.full_cache_layers:
-            next_full = (layer + 1) in self.full_cache_layers if layer + 1 < num_layers else True
-            return "full" if next_full else "planner"
-        return "subset"
+from typing import Any, Mapping, Optional
 
 
 @dataclass(frozen=True)
@@ -70,11 +28,9 @@ class EngineConfig:
     dtype: str = "bfloat16"            # "bfloat16" | "float32"
     max_tokens_per_step: int = 2048
     cuda_graph_decode: bool = False
-    selective: Optional[SelectiveCacheConfig] = None
-    rope_interleaved: bool = False
-    seed: int = 123
-    check_kernel_errors: bool = True   # read the kernels' error flag after every step
+    check_kernel_errors: bool = True   # read the kernels' error record with every step's result
     shuffle_pages: Optional[int] = None  # seed: hand pages out in a shuffled order
+    options: Mapping[str, Any] = field(default_factory=dict)   # for the architecture's specification builder
 
     def __post_init__(self):
         if self.dtype not in ("bfloat16", "float32"):
@@ -83,6 +39,11 @@ class EngineConfig:
             raise ValueError(f"page_size must be a power of two of at most 128, got {self.page_size}")
         if self.max_batch < 1 or self.max_seq_len < 1 or self.max_tokens_per_step < 1:
             raise ValueError("max_batch, max_seq_len and max_tokens_per_step must be positive")
+
+    def option(self, name: str, default=None):
+        """An architecture-specific option (None or ``default`` when it was not given)."""
+        v = self.options.get(name)
+        return default if v is None else v
 
     @property
     def pages_per_request(self) -> int:

@@ -1,0 +1,52 @@
+"""DELTA's selective cache as an option of the Yi model specification.
+
+The reference's scripts put these on ``model.config`` (tests/reasoni.py:327-335); the
+names are its command-line names (tests/reasoni.py:251-262).  The generic engine does
+not know them: they travel in ``EngineConfig.options["selective_cache"]`` to the
+function that builds the model specification, which gives every attention layer its role.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class SelectiveCacheConfig:
+    """DELTA: which layers read the whole cache and how many pages the others read.
+
+    ``full_cache_layers`` are layer indices (tests/reasoni.py:251).  A full
+    layer followed by a non-full layer scores the pages and chooses
+    ``subset_cache_size`` of them for the layers after it
+    (DELTA/Engine/DELTA/model.py:177-194).  The last ``L`` pages are always
+    chosen (page_selector_v2.py:120-123); ``L`` is clamped to
+    ``subset_cache_size``.  A request uses the subset once
+    pages / min(pages, subset_cache_size) > ``compression_ratio``
+    (backend.py:1893-1897, decided per request here, per batch there).
+    """
+    full_cache_layers: tuple = ()
+    subset_cache_size: int = 1024
+    compression_ratio: float = 1.0
+    L: int = 8
+    position_bias: float = 1e-7
+
+    def __post_init__(self):
+        object.__setattr__(self, "full_cache_layers", tuple(sorted(set(int(i) for i in self.full_cache_layers))))
+        if self.subset_cache_size < 1:
+            raise ValueError("subset_cache_size must be at least 1")
+        if self.L < 1:
+            raise ValueError("L must be at least 1: the page that holds the newest token is always read")
+        if self.compression_ratio < 1.0:
+            raise ValueError("compression_ratio must be at least 1")
+
+    @property
+    def keep_last(self) -> int:
+        return min(self.L, self.subset_cache_size)
+
+    def role(self, layer: int, num_layers: int) -> str:
+        """'full', 'planner' (full, and it chooses pages for what follows) or 'subset'."""
+        if not self.full_cache_layers:
+            return "full"
+        if layer in self.full_cache_layers:
+            next_full = (layer + 1) in self.full_cache_layers if layer + 1 < num_layers else True
+            return "full" if next_full else "planner"
+        return "subset"

@@ -579,7 +579,10 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     DK_REQUIRE(make_tensor_map_bf16_4d(&map_run, p.kv, dims, strides, p.ps, TILE / p.ps),
                "attention_decode: cannot encode the tensor map of runs of pages");
   }
-  static size_t configured = 0;
+  static size_t configured_on[64] = {0};     // per device: the attribute belongs to the device's copy of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_on[dev & 63];
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
@@ -602,6 +605,32 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
 extern "C" long long dk_attention_decode_scratch_floats(int rows, int H, int hd, int splits) {
   if (splits <= 1) return 0;
   return (long long)rows * H * splits * (hd + 2);
+}
+
+// Blocks of the decode kernel that one SM holds at once for these sizes (registers and shared
+// memory decide), asked of the runtime for the current device; 0 with the error set on failure.
+extern "C" int dk_attention_decode_blocks_per_sm(int H, int KV, int hd, int block_entries) {
+  if (KV <= 0 || (hd != 64 && hd != 128)) return 0;
+  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)3 * block_entries * sizeof(int);
+  const size_t merge_bytes = (size_t)NWARPS * 16 * hd * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
+  const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+  const bool low = H / KV <= 8;
+  int n = 0;
+  cudaError_t e;
+  if (hd == 64) {
+    auto k = low ? attention_decode_kernel<64, true, false> : attention_decode_kernel<64, false, false>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, NTHREADS, smem);
+  } else {
+    auto k = low ? attention_decode_kernel<128, true, false> : attention_decode_kernel<128, false, false>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, NTHREADS, smem);
+  }
+  if (e != cudaSuccess) {
+    dk_set_error("attention_decode: occupancy query failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  return n;
 }
 
 // 1 when the fast kernel takes these sizes, else 0 (the caller then uses the plain kernel).

@@ -96,13 +96,15 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
                                                     const float* __restrict__ temperature, const float* __restrict__ top_p,
                                                     const unsigned long long* __restrict__ seeds,
                                                     const int* __restrict__ positions, int* __restrict__ out,
-                                                    int* __restrict__ out_copy) {
+                                                    const int* __restrict__ status) {
   __shared__ float s_val[33];
   __shared__ int s_idx[33];
   __shared__ float s_scan[ST];
   __shared__ float s_red[34];
   __shared__ int s_pick;
   const int r = blockIdx.x;
+  // the kernels' error record as it stands when the step's last kernel runs, behind the tokens
+  if (status != nullptr && r == 0 && threadIdx.x < 4) out[gridDim.x + threadIdx.x] = status[threadIdx.x];
   const float* row = logits + (size_t)r * ldl;
   const float temp = temperature ? temperature[r] : 0.f;
   float mx;
@@ -110,7 +112,6 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
   if (!(temp > 0.f)) {
     if (threadIdx.x == 0) {
       out[r] = amax;
-      if (out_copy) out_copy[r] = amax;
     }
     return;
   }
@@ -209,16 +210,16 @@ __global__ void __launch_bounds__(ST) sample_kernel(const float* __restrict__ lo
     }
     if (pick < 0) pick = last >= 0 ? last : amax;
     out[r] = pick;
-    if (out_copy) out_copy[r] = pick;
+
   }
 }
 }  // namespace
 
 extern "C" int dk_sample(const float* logits, int ldl, int R, int V, const float* temperature, const float* top_p,
-                         const unsigned long long* seeds, const int* positions, int* out, int* out_copy,
+                         const unsigned long long* seeds, const int* positions, int* out, const int* status,
                          cudaStream_t stream) {
   if (R == 0) return 0;
   DK_REQUIRE(R > 0 && V > 0 && ldl >= V, "sample: bad sizes R=%d V=%d ld=%d", R, V, ldl);
-  sample_kernel<<<R, ST, 0, stream>>>(logits, ldl, V, temperature, top_p, seeds, positions, out, out_copy);
+  sample_kernel<<<R, ST, 0, stream>>>(logits, ldl, V, temperature, top_p, seeds, positions, out, status);
   return dk_check_launch("sample");
 }

@@ -16,16 +16,21 @@ Results have the reference's keys (scheduler.py:166-182) plus the generated ids.
 """
 from __future__ import annotations
 
+import json
 import time
+from pathlib import Path
 from types import SimpleNamespace
 from typing import List, Optional, Sequence
 
 import torch
 
-from ..config.engine_config import EngineConfig, SelectiveCacheConfig
-from ..sampling.sampler import SamplingParams, sample
+from ..config.engine_config import EngineConfig
+from ..config.selective_cache import SelectiveCacheConfig
+from ..kernels import ops
+from ..parts.base import ROW_DECODE
+from ..sampling.sampler import SamplingParams
 from .scheduler import PlannedRow, Scheduler
-from .step import ModelRunner, RowInput
+from .step import ModelRunner, RowInput, StepResult
 
 
 class LMBackend:
@@ -56,6 +61,9 @@ class LMBackend:
         # of step N, step N + 1 already runs with those tokens taken on the device.  See _run_ahead.
         self.run_ahead = True
         self._ahead = None
+        # called as on_step_logits(plan, logits) after every step, with the float32 logits [sampled rows, vocab]
+        # on the device in the order of the plan's sampling rows; while it is set no step is launched ahead
+        self.on_step_logits = None
 
     # ---- set-up -------------------------------------------------------------
     def load_model(self, model_dir=None, *, config_json: Optional[dict] = None, seed: Optional[int] = None, **unused):
@@ -72,7 +80,11 @@ class LMBackend:
                      num_pages: Optional[int] = None, max_tokens_per_step: int = 2048,
                      enable_selective_cache: Optional[bool] = None, full_cache_layers=None,
                      subset_cache_size: Optional[int] = None, compression_ratio: Optional[float] = None,
-                     L: Optional[int] = None, check_kernel_errors: bool = False, rope_interleaved: bool = False):
+                     L: Optional[int] = None, check_kernel_errors: bool = True, rope_interleaved: bool = False,
+                     shuffle_pages: Optional[int] = None):
+        """``check_kernel_errors``: the kernels' error record (a bad page id, token id or position
+        that a kernel skipped, a wait inside a kernel that ran out) travels to the host with every
+        step's tokens and raises there; this costs no synchronisation."""
         o = self.options
         if enable_selective_cache is not None:
             o.enable_selective_cache = enable_selective_cache
@@ -90,13 +102,14 @@ class LMBackend:
                                              compression_ratio=float(o.compression_ratio), L=o.L)
         cfg = EngineConfig(max_batch=max_batch_size, max_seq_len=max_seq_length, page_size=page_size, num_pages=num_pages,
                            dtype=self.dtype, max_tokens_per_step=max_tokens_per_step,
-                           cuda_graph_decode=self.cuda_graph_decode, selective=selective,
-                           check_kernel_errors=check_kernel_errors, rope_interleaved=rope_interleaved)
+                           cuda_graph_decode=self.cuda_graph_decode, check_kernel_errors=check_kernel_errors,
+                           shuffle_pages=shuffle_pages,
+                           options=dict(selective_cache=selective, rope_interleaved=rope_interleaved))
         self.engine_config = cfg
         self.runner = ModelRunner(self._model_dir, engine_config=cfg, config_json=self._config_json, seed=self._seed,
                                   device=self.device)
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch_size, max_tokens_per_step=max_tokens_per_step,
-                                   selective=selective is not None)
+                                   decode_singly=self.runner.model.decode_rows_differ())
 
     # ---- requests ---------------------------------------------------------------
     def add_requests(self, input_ids_list, max_lengths, eot_token_ids: Sequence[int] = (), *, temperature=0.0, top_p=1.0,
@@ -114,10 +127,18 @@ class LMBackend:
 
     # ---- the loop -----------------------------------------------------------------
     def step(self) -> List:
-        """One scheduler step: plan, run, sample, book.  Returns the requests that finished."""
+        """One scheduler step: plan, run, sample, book.  Returns the requests that finished.
+
+        With ``record_timings`` every step is timed and the device is waited for at its end (so no
+        step is launched ahead of the host); the record has the reference's five names
+        (backend.py:1522-1533): ``collect_pages`` the host's filling of the staging block (block
+        tables, positions, sampling parameters), ``plan`` the scheduler's decisions and page
+        bookkeeping, ``model_forward`` the device time from the staging copy to the sampled tokens,
+        ``postprocess`` asking for the tokens on the host, ``step_total`` the wall clock of the step."""
         sch, runner = self.scheduler, self.runner
         t0 = time.perf_counter()
         plan = sch.schedule()
+        t_plan = time.perf_counter()
         if not plan:
             self._ahead = None
             if sch.has_work() and not sch.running:
@@ -127,68 +148,86 @@ class LMBackend:
                 return [r]
             return []
         ahead, self._ahead = self._ahead, None
-        reuse = None if (ahead is None or self.record_timings) else self._match_ahead(plan, ahead)
+        reuse = None if (ahead is None or self.record_timings or self.on_step_logits) else self._match_ahead(plan, ahead)
         ev = None
+        t_staged = t_plan
         if reuse is not None:
             # this step was launched while the host waited for the step before: only its result is read
-            tokens, read = ahead["tokens"], ahead["read"]
+            result, read = ahead["result"], ahead["read"]
         else:
             rows = []
             for x in plan:
                 r = x.request
                 toks = r.tokens[x.start:x.start + x.count]
                 rows.append(RowInput(r.slot, toks, x.start, [x.count - 1] if x.samples else [],
-                                     selective=bool(sch.selective and x.decode), sampling=r.sampling))
+                                     flags=ROW_DECODE if x.decode else 0, sampling=r.sampling))
             if self.record_timings:
                 # the first event is recorded when the host has filled the staging buffer, right before
                 # the step's first copy, so that the device time holds no wait for the host
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-                runner.on_device_work = ev[0].record
-            logits, tokens = runner.step_and_sample(rows)
+                staged = []
+
+                def on_device_work():
+                    staged.append(time.perf_counter())
+                    ev[0].record()
+                runner.on_device_work = on_device_work
+            logits, _ = runner.step_and_sample(rows)
             runner.on_device_work = None
+            if self.on_step_logits is not None:
+                self.on_step_logits(plan, logits)
+            result = runner.step_result
             if ev:
+                t_staged = staged[0] if staged else t_plan
                 ev[1].record()
-            read = self._start_read(tokens)
+            read = self._start_read(result)
             if ev:
                 ev[2].record()      # after the copy to the host is asked for, before the host waits for it
         if reuse is None or reuse == list(range(len(ahead["rows"]))):
-            self._run_ahead(plan, tokens)
+            self._run_ahead(plan, result)
         new_tokens = self._finish_read(read)
         if reuse is not None:
             new_tokens = [new_tokens[i] for i in reuse]
         if ev:
             torch.cuda.synchronize()
-            self.step_timings.append(dict(plan_ms=0.0, model_forward_ms=ev[0].elapsed_time(ev[1]),
+            self.step_timings.append(dict(step=len(self.step_timings) + 1, collect_pages_ms=(t_staged - t_plan) * 1e3,
+                                          plan_ms=(t_plan - t0) * 1e3, model_forward_ms=ev[0].elapsed_time(ev[1]),
                                           postprocess_ms=ev[1].elapsed_time(ev[2]),
                                           step_total_ms=(time.perf_counter() - t0) * 1e3,
                                           active_bsz=len(plan), tokens=sum(x.count for x in plan),
                                           total_pages=sum(runner.cache.pages_in_use().values())))
         return sch.complete(plan, new_tokens)
 
-    def _start_read(self, tokens: torch.Tensor):
+    def _start_read(self, result: Optional[StepResult]):
         """Starts the device-to-host read of a step's result, through pinned memory (two buffers
-        in turns: the read of the step that runs ahead is started before this one is finished)."""
-        n = tokens.shape[0]
-        if n == 0:
+        in turns: the read of the step that runs ahead is started before this one is finished).
+        The kernels' error record comes with the tokens."""
+        if result is None:
             return None
+        n = result.tensor.shape[0]
         self._read_turn ^= 1
         buf = self._host_tokens[self._read_turn]
         if buf is None or buf.numel() < n:
             buf = self._host_tokens[self._read_turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
-        buf[:n].copy_(tokens, non_blocking=True)
+        buf[:n].copy_(result.tensor, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return buf, done, n
+        return buf, done, result
 
-    @staticmethod
-    def _finish_read(read) -> List[int]:
+    def _finish_read(self, read) -> List[int]:
         if read is None:
             return []
-        buf, done, n = read
+        buf, done, result = read
         done.synchronize()      # waits for this step only, not for the one launched after it
-        return buf[:n].tolist()
+        if self.engine_config.check_kernel_errors:
+            code, a, b, c = buf[result.status_at:result.status_at + 4].tolist()
+            if code != 0:
+                self._ahead = None
+                torch.cuda.synchronize()
+                self.runner.err.zero_()
+                raise ops.KernelError(ops.error_text(code, a, b, c))
+        return buf[:result.n_tokens].tolist()
 
-    def _run_ahead(self, plan, tokens: torch.Tensor) -> None:
+    def _run_ahead(self, plan, result: Optional[StepResult]) -> None:
         """Launches the next decode step before the host has read this one's tokens.
 
         Only when the next step is certain but for stop tokens: every row of this step decodes one
@@ -200,7 +239,7 @@ class LMBackend:
         same values."""
         from ..cache.page_pool import OutOfPages
         sch, runner = self.scheduler, self.runner
-        if not (self.run_ahead and self.cuda_graph_decode) or self.record_timings or sch.waiting or not plan:
+        if not (self.run_ahead and self.cuda_graph_decode) or self.record_timings or self.on_step_logits or sch.waiting or not plan or result is None:
             return
         if not runner.decode_graph_ready(len(plan)):
             return
@@ -219,10 +258,10 @@ class LMBackend:
                 runner.cache.grow(x.request.slot, x.start + 2)
         except OutOfPages:
             return
-        rows = [RowInput(x.request.slot, [0], x.start + 1, [0], selective=bool(sch.selective), sampling=x.request.sampling)
-                for x in plan]
-        _, nxt = runner.step_and_sample(rows, tokens_from=tokens)
-        self._ahead = dict(rows=[(x.request.slot, x.start + 1) for x in plan], tokens=nxt, read=self._start_read(nxt))
+        rows = [RowInput(x.request.slot, [0], x.start + 1, [0], flags=ROW_DECODE, sampling=x.request.sampling) for x in plan]
+        runner.step_and_sample(rows, tokens_from=result.tensor)
+        nxt = runner.step_result
+        self._ahead = dict(rows=[(x.request.slot, x.start + 1) for x in plan], result=nxt, read=self._start_read(nxt))
 
     @staticmethod
     def _match_ahead(plan, ahead) -> Optional[List[int]]:
@@ -249,7 +288,31 @@ class LMBackend:
                 break
         torch.cuda.synchronize()
         self.loop_time = time.perf_counter() - self.loop_start
+        if self.engine_config.check_kernel_errors:
+            self.runner.check_errors()
         return self.get_detailed_results()
+
+    def save_step_timings(self, folder="logs", meta: Optional[dict] = None) -> Optional[Path]:
+        """Writes the per-step records of a run with ``record_timings`` to
+        ``<folder>/step_timings_<time>.json`` as {"meta": ..., "steps": [...]}, the reference's file
+        (backend.py:2240-2285).  Returns the path, or None when nothing was recorded."""
+        if not self.step_timings:
+            return None
+        folder = Path(folder)
+        folder.mkdir(parents=True, exist_ok=True)
+        path = folder / f"step_timings_{time.strftime('%Y%m%d_%H%M%S')}.json"
+        names = ["collect_pages", "plan", "model_forward", "postprocess", "step_total"]
+        n = len(self.step_timings)
+        summary = {k: dict(avg_ms=sum(r[k + "_ms"] for r in self.step_timings) / n,
+                           total_ms=sum(r[k + "_ms"] for r in self.step_timings)) for k in names}
+        cfg = self.engine_config
+        info = dict(steps=n, dtype=cfg.dtype, max_batch=cfg.max_batch, max_seq_len=cfg.max_seq_len, page_size=cfg.page_size,
+                    cuda_graph_decode=cfg.cuda_graph_decode, selective_cache=cfg.option("selective_cache") is not None,
+                    graph_captures=self.runner.graph_captures, graph_replays=self.runner.graph_replays,
+                    graph_fallbacks=dict(self.runner.graph_fallbacks), summary=summary)
+        info.update(meta or {})
+        path.write_text(json.dumps({"meta": info, "steps": self.step_timings}, indent=2))
+        return path
 
     def get_detailed_results(self) -> List[dict]:
         res = self.scheduler.results()

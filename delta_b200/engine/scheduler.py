@@ -15,8 +15,12 @@ everyone's decode token, and sizes the pool so that it can never run out
     its whole prompt and one more token, beside what the step already promised;
   * when a running request cannot grow, the youngest running request is preempted:
     its pages are given back, it returns to the head of the queue and what it had
-    computed is computed again (prompt and generated tokens as one prompt) once it
-    is admitted again; a request that could not fit even alone fails.
+    computed is computed again once it is admitted again; a request that could not
+    fit even alone fails.  What is computed again gives the logits of the first time:
+    when the model treats decode rows like any other (``decode_singly`` False) prompt
+    and generated tokens run as one prompt; when some part treats them otherwise (page
+    selection applies to decode rows only) the prompt runs in portions and every
+    generated token again as a decode row of its own, one per step, unsampled.
 """
 from __future__ import annotations
 
@@ -65,15 +69,16 @@ class PlannedRow:
     start: int          # position of the first token of this share
     count: int
     samples: bool       # the last token of the share yields a new token
-    decode: bool        # a single token at or after the prompt's end
+    decode: bool        # a single token at or after the prompt's end (a decode row; ``samples`` False: one that is computed again)
 
 
 class Scheduler:
-    def __init__(self, cache, *, max_batch: int, max_tokens_per_step: int, selective: bool = False, clock=time.perf_counter):
+    def __init__(self, cache, *, max_batch: int, max_tokens_per_step: int, decode_singly: bool = False, clock=time.perf_counter):
         self.cache = cache
         self.max_batch = int(max_batch)
         self.budget = int(max_tokens_per_step)
-        self.selective = bool(selective)
+        # True: tokens at or after a prompt's end never run inside a prompt portion (see the module text)
+        self.decode_singly = bool(decode_singly)
         self.clock = clock
         self.requests: List[Request] = []
         self.waiting: List[Request] = []
@@ -125,24 +130,31 @@ class Scheduler:
         """Chooses what runs in the next step and books the pages for it."""
         budget = self.budget
         rows: List[PlannedRow] = []
-        # 1. one token for every request that is decoding
-        hold = (not self.decode_while_prefill) and (bool(self.waiting) or any(
-            q.total_len - q.computed > 1 for q in self.running))
+        # 1. one token for every request that is decoding (or computing a decode position again)
+        # With prompts first, decoding waits only while a prompt is really under way or about to be: a
+        # waiting request that cannot be admitted (no slot, no pages) must not stop those that can end.
+        hold = (not self.decode_while_prefill) and (
+            any(q.computed < q.total_len - 1 for q in self.running)
+            or bool(self.waiting and len(self.running) < self.max_batch and self.cache.free_slots > 0
+                    and self._can_admit(self.waiting[0])))
         for r in sorted(self.running, key=lambda q: q.admitted_order):
-            if hold and r.output:
+            last = r.computed == r.total_len - 1
+            if hold and last and r.output:
                 continue
-            if r.status != RUNNING or r.computed != r.total_len - 1 or budget < 1:
+            again = self.decode_singly and len(r.prompt) <= r.computed < r.total_len - 1
+            if r.status != RUNNING or not (last or again) or budget < 1:
                 continue
-            if not self._grow_or_preempt(r, r.total_len, protect=[x.request for x in rows]):
+            if not self._grow_or_preempt(r, r.computed + 1, protect=[x.request for x in rows]):
                 continue
-            rows.append(PlannedRow(r, r.computed, 1, True, decode=r.computed >= len(r.prompt)))
+            rows.append(PlannedRow(r, r.computed, 1, samples=last, decode=r.computed >= len(r.prompt)))
             budget -= 1
-        # 2. portions of prompts that are under way (after a preemption a prompt includes what was generated)
+        # 2. portions of prompts that are under way (after a preemption a prompt includes what was
+        #    generated, unless decode positions run singly)
         for r in sorted(self.running, key=lambda q: q.admitted_order):
             if r.status != RUNNING or budget < 1 or any(x.request is r for x in rows):
                 continue
-            left = r.total_len - r.computed
-            if left <= 1 and r.computed == r.total_len - 1:
+            left = self._portion_end(r) - r.computed
+            if left < 1 or r.computed == r.total_len - 1:
                 continue
             count = min(left, budget)
             if not self._grow_or_preempt(r, r.computed + count, protect=[x.request for x in rows]):
@@ -163,11 +175,15 @@ class Scheduler:
             if r.start_time is None:
                 r.start_time = self.clock()
             self.running.append(r)
-            count = min(r.total_len, budget)
+            count = min(self._portion_end(r), budget)
             self.cache.grow(r.slot, count)
             rows.append(PlannedRow(r, 0, count, samples=(count == r.total_len), decode=False))
             budget -= count
         return rows
+
+    def _portion_end(self, r: Request) -> int:
+        """Where the tokens end that may run as prompt portions."""
+        return len(r.prompt) if self.decode_singly else r.total_len
 
     def _can_admit(self, r: Request) -> bool:
         """Room for the whole prompt and one more token in every group."""

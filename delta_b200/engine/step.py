@@ -39,8 +39,18 @@ class RowInput:
     tokens: Sequence[int]
     start_pos: int
     want: Sequence[int] = ()
-    selective: bool = False   # a decode token that DELTA's page selection applies to
+    flags: int = 0            # bits for the parts to interpret (parts.base.ROW_DECODE: a single token at or after the prompt's end)
     sampling: Optional[object] = None   # SamplingParams for the tokens sampled at ``want`` (None: greedy)
+
+
+@dataclass
+class StepResult:
+    """What a sampled step leaves for the host: ``tensor`` [rows + 4] int32 on the device holds the
+    new tokens (the first ``n_tokens`` belong to requests) and, from ``status_at`` on, the four
+    ints of the kernels' error record as the step's last kernel saw them."""
+    tensor: torch.Tensor
+    n_tokens: int
+    status_at: int
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -86,7 +96,7 @@ class ModelRunner:
         self.model = Model(self.spec)
         specs = self.model.tensor_specs()
         if model_dir is not None:
-            tensors = load_tensors(model_dir, specs, self.dtype, self.device)
+            tensors = load_tensors(model_dir, specs, self.dtype, self.device, ignorable=self.spec.ignorable_tensors)
         else:
             tensors = random_tensors(specs, 0 if seed is None else seed, self.dtype, self.device)
         self.model.bind(tensors)
@@ -100,14 +110,15 @@ class ModelRunner:
         self._staging = []      # ring of (pinned buffer, event)
         self.on_device_work = None   # called once per step right before its first device operation (for timing)
         self._staging_next = 0
-        self.plain_products = False
-        self.plain_attention = False
+        self.plain_kernels = set()   # "products", "attention": take the slow plain kernels (for comparisons)
         self.capture: Optional[dict] = None
         self.steps_run = 0
         self.last_staging_bytes = 0
         self._graphs: Dict[int, dict] = {}
         self.graph_captures = 0
         self.graph_replays = 0
+        self.graph_fallbacks: Dict[str, int] = {}     # why decode steps ran eagerly although graphs are on: reason -> count
+        self.step_result: Optional[StepResult] = None
 
     # ---- staging ---------------------------------------------------------------
     def _pinned(self, n: int):
@@ -145,8 +156,6 @@ class ModelRunner:
                 raise ValueError("a row of a step needs at least one token")
             if not self.cache.is_live(r.slot):
                 raise ValueError(f"slot {r.slot} is not live")
-            if r.selective and n != 1:
-                raise ValueError("page selection applies to single decode tokens only")
             for w in r.want:
                 if not (0 <= w < n):
                     raise ValueError(f"wanted place {w} lies outside the row's {n} tokens")
@@ -173,7 +182,7 @@ class ModelRunner:
         put("tok_row", np.repeat(np.arange(B, dtype=np.int32), q_lens))
         put("tok_pos", np.concatenate([np.arange(r.start_pos, r.start_pos + n, dtype=np.int32) for r, n in zip(rows, q_lens)]))
         put("row_slot", [r.slot for r in rows])
-        put("row_flags", [1 if r.selective else 0 for r in rows])
+        put("row_flags", [int(r.flags) for r in rows])
         put("row_q_start", q_start)
         put("row_q_len", q_lens)
         put("row_pos_start", [r.start_pos for r in rows])
@@ -196,17 +205,18 @@ class ModelRunner:
             a, n = layout["bt:" + g]
             host[a:a + n] = self.cache.groups[g].table[slots, :max_pages].reshape(-1)
 
-    def _context(self, dev: torch.Tensor, layout: dict, rows, q_lens, q_start, wants, max_pages, max_seq) -> StepContext:
+    def _context(self, dev: torch.Tensor, layout: dict, rows, q_lens, q_start, wants, max_pages, max_seq,
+                 replayable: bool = False) -> StepContext:
         B = len(rows)
         sections = {k: dev[a:a + n] for k, (a, n) in layout.items() if not k.startswith("bt:")}
         block_tables = {g: dev[layout["bt:" + g][0]:layout["bt:" + g][0] + B * max_pages].view(B, max_pages)
                         for g in self.cache.groups}
-        info = dict(max_pages=max_pages, any_selective=any(r.selective for r in rows),
-                    decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens) if q_lens else 0, max_seq_len=max_seq,
+        info = dict(max_pages=max_pages, decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens) if q_lens else 0, max_seq_len=max_seq,
                     rows=rows, q_lens=q_lens, q_start=q_start, wants=wants)
         return StepContext(device=self.device, dtype=self.dtype, cache=self.cache, sections=sections,
                            block_tables=block_tables, host=info, err=self.err, scratch_pool=self._scratch,
-                           plain_products=self.plain_products, plain_attention=self.plain_attention, capture=self.capture)
+                           plain_kernels=self.plain_kernels, replayable=replayable, capture=None if replayable else self.capture,
+                           max_rows=self.cfg.max_batch, max_step_tokens=self.cfg.max_tokens_per_step)
 
     def build_context(self, rows: List[RowInput]) -> StepContext:
         """Fills the staging buffer for these rows and copies it to the device."""
@@ -239,13 +249,15 @@ class ModelRunner:
             ops.raise_if_error(self.err)
         return logits
 
-    def _sample(self, ctx: StepContext, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _sample(self, ctx: StepContext, logits: torch.Tensor) -> torch.Tensor:
+        """One token per wanted place, and after them the four ints of the kernels' error
+        record as the step's last kernel saw them: [R + 4] int32.  Whoever reads the tokens
+        on the host gets the step's status with them, without a synchronisation of its own."""
         R = logits.shape[0]
-        out = out if out is not None else torch.empty(R, dtype=torch.int32, device=self.device)
-        if R:
-            s = ctx.sampling_sections
-            ops.sample(logits, out, temperature=s["samp_temp"].view(torch.float32), top_p=s["samp_top_p"].view(torch.float32),
-                       seeds=s["samp_seed"].view(torch.int64), positions=s["samp_pos"])
+        out = torch.empty(R + 4, dtype=torch.int32, device=self.device)
+        s = ctx.sampling_sections
+        ops.sample(logits, out, temperature=s["samp_temp"].view(torch.float32), top_p=s["samp_top_p"].view(torch.float32),
+                   seeds=s["samp_seed"].view(torch.int64), positions=s["samp_pos"], err=self.err)
         return out
 
     def graph_batch(self, batch: int) -> int:
@@ -268,12 +280,15 @@ class ModelRunner:
 
     def step_and_sample(self, rows: List[RowInput], tokens_from: Optional[torch.Tensor] = None):
         """One batch, and one new token for every wanted place (greedy, or as the row's
-        ``sampling`` says).  Returns (logits, tokens), both on the device.  A step in which
+        ``sampling`` says).  Returns (logits, tokens), both on the device; ``step_result`` holds
+        the tokens followed by the kernels' error record for a single read by the host
+        (``StepResult``), and nothing here waits for the device.  A step in which
         every row brings one token is replayed from a CUDA graph when the engine was set up
         with ``cuda_graph_decode``.  ``tokens_from``: a device tensor with one token per row that
         takes the place of the rows' own tokens (the tokens the step before sampled, which the
         host has not read yet); only for steps that ``decode_graph_ready`` says are replayed."""
         if not rows:
+            self.step_result = None
             return (torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device),
                     torch.empty(0, dtype=torch.int32, device=self.device))
         if self.cfg.cuda_graph_decode and all(len(r.tokens) == 1 and list(r.want) == [0] for r in rows):
@@ -282,21 +297,25 @@ class ModelRunner:
             raise ValueError("tokens from the device are taken by captured decode steps only")
         ctx = self.build_context(rows)
         logits = self.model.forward(ctx)
-        tokens = self._sample(ctx, logits)
+        out = self._sample(ctx, logits)
+        R = logits.shape[0]
+        self.step_result = StepResult(out, R, R)
         self.steps_run += 1
-        if self.cfg.check_kernel_errors:
-            ops.raise_if_error(self.err)
-        return logits, tokens
+        return logits, out[:R]
+
+    def check_errors(self) -> None:
+        """Reads the kernels' error record (waits for the device) and raises if it is set."""
+        ops.raise_if_error(self.err)
 
     # ---- decode steps from a CUDA graph ---------------------------------------------
     def _graph_step(self, rows: List[RowInput], tokens_from: Optional[torch.Tensor] = None):
-        """Replays the captured decode step for this batch size.  All metadata lives in one
+        """Replays the recorded decode step for this batch size.  All metadata lives in one
         device buffer of fixed layout that a single copy refreshes before the replay; block
-        tables have their full width, the attention grid is the one sized for the longest
-        request the engine allows, so nothing in the graph depends on the step.
+        tables have their full width and the parts are told that the step is replayable, so
+        nothing in the graph depends on the step.  When recording fails, this batch size runs
+        eagerly from then on and the reason is counted in ``graph_fallbacks``.
         Reference: backend.py:974-1001 (when a graph is used), 1119-1162 (two warm-up runs,
-        then capture)."""
-        from .attention_dispatch import decode_splits
+        then capture), 1138-1150 and 1174-1181 (failure: eager, with counted reasons)."""
         n_real = len(rows)
         self._check_rows(rows)
         # The step is captured for a rounded-up batch size; the spare rows decode position 0 of
@@ -309,7 +328,7 @@ class ModelRunner:
         if g is None:
             layout, size = self._layout(B, B, B, max_pages)
             g = dict(layout=layout, size=size, dev=torch.zeros(size, dtype=torch.int32, device=self.device), graph=None,
-                     warm=0)
+                     warm=0, failed=None)
             self._graphs[B] = g
         layout, size, dev = g["layout"], g["size"], g["dev"]
         idx, pinned = self._pinned(size)
@@ -326,39 +345,41 @@ class ModelRunner:
             dev[a:a + n_real].copy_(tokens_from[:n_real])      # device to device, in stream order before the replay
 
         def run():
-            ctx = self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, self.cache.max_seq_len)
-            ctx.any_selective = self.cfg.selective is not None
-            ctx.capture = None
-            kvh = max((cs.kv_heads for cs in self.model.cache_specs().values()), default=1)
-            ctx.fixed_decode_splits = decode_splits(B, kvh, self.cache.max_seq_len)
+            ctx = self._context(dev, layout, rows, q_lens, q_start, wants, max_pages, self.cache.max_seq_len, replayable=True)
             logits = self.model.forward(ctx)
-            tokens = self._sample(ctx, logits)
-            return logits, tokens
+            return logits, self._sample(ctx, logits)
 
-        if g["graph"] is None:
-            if g["warm"] < 2:           # eager runs first: they size every scratch buffer
-                g["warm"] += 1
-                logits, tokens = run()
-                self.steps_run += 1
-                return logits[:n_real], tokens[:n_real]
-            # the eager runs have sized the scratch buffers; now record the same launches
+        if g["graph"] is None and not g["failed"] and g["warm"] >= 2:
+            # two eager runs have sized the working buffers; now record the same launches
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
             l0 = ops.launch_count()
-            with torch.cuda.graph(graph):
-                g["out"] = run()
-            g["graph"] = graph
-            g["launches"] = ops.launch_count() - l0     # kernels recorded, not run
-            ops.count_launch(-g["launches"])
-            self.graph_captures += 1
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    g["out"] = run()
+                g["graph"] = graph
+                g["launches"] = ops.launch_count() - l0     # kernels recorded, not run
+                self.graph_captures += 1
+            except Exception as e:  # noqa: BLE001  (whatever stops the recording: this size stays eager)
+                g["failed"] = f"capture failed: {type(e).__name__}"
+                g["error"] = str(e)
+                torch.cuda.synchronize()
+            ops.count_launch(l0 - ops.launch_count())
+        if g["graph"] is None:
+            g["warm"] += 1
+            if g["failed"]:
+                self.graph_fallbacks[g["failed"]] = self.graph_fallbacks.get(g["failed"], 0) + 1
+            logits, out = run()
+            self.steps_run += 1
+            self.step_result = StepResult(out, n_real, B)
+            return logits[:n_real], out[:n_real]
         g["graph"].replay()
         ops.count_launch(g["launches"])
         self.steps_run += 1
         self.graph_replays += 1
-        if self.cfg.check_kernel_errors:
-            ops.raise_if_error(self.err)
-        logits, tokens = g["out"]
-        return logits[:n_real], tokens[:n_real]
+        logits, out = g["out"]
+        self.step_result = StepResult(out, n_real, B)
+        return logits[:n_real], out[:n_real]
 
     # ---- convenience used by replay and tests --------------------------------------
     def run_rows(self, rows: List[RowInput]) -> torch.Tensor:

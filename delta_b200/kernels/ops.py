@@ -62,11 +62,16 @@ _ERR_TEXT = {1: "page id out of range (token {0}, logical page {1}, page id {2})
              4: "a wait inside a kernel ran out (block {0}, part {1}, {2} steps); its result was not stored"}
 
 
+def error_text(code: int, a: int, b: int, c: int) -> str:
+    return "a kernel met a bad index and skipped it: " + _ERR_TEXT.get(code, "code {3}").format(a, b, c, code)
+
+
 def raise_if_error(err: torch.Tensor) -> None:
+    """Reads the record (this waits for the device), clears it and raises when it is set."""
     code, a, b, c = err.tolist()
     if code != 0:
         err.zero_()
-        raise KernelError("a kernel met a bad index and skipped it: " + _ERR_TEXT.get(code, "code {3}").format(a, b, c, code))
+        raise KernelError(error_text(code, a, b, c))
 
 
 # ---------------------------------------------------------------------------
@@ -188,6 +193,20 @@ def attention_decode_supported(dtype, H, KV, hd, ps) -> bool:
     if dtype != torch.bfloat16:
         return False
     return bool(_l.load().dk_attention_decode_supported(BF16, H, KV, hd, ps))
+
+
+_decode_occupancy = {}
+
+
+def attention_decode_blocks_per_sm(H, KV, hd, block_entries) -> int:
+    """Blocks of the decode kernel one SM of the current device holds at once (asked of the runtime once)."""
+    key = (torch.cuda.current_device(), H, KV, hd, block_entries)
+    if key not in _decode_occupancy:
+        n = int(_l.load().dk_attention_decode_blocks_per_sm(H, KV, hd, block_entries))
+        if n < 1:
+            raise KernelError("attention_decode: " + _l.load().dk_last_error().decode("utf-8", "replace"))
+        _decode_occupancy[key] = n
+    return _decode_occupancy[key]
 
 
 def attention_decode_scratch_floats(rows, H, hd, splits) -> int:
@@ -315,12 +334,19 @@ def select_pages(scores, row_slot, row_flags, row_pos_start, row_q_len, sel_page
                                        sel_pages.shape[1], keep_last, ps, float(bias), float(ratio), _stream()), "select_pages")
 
 
-def sample(logits, out, temperature=None, top_p=None, seeds=None, positions=None, out_copy=None):
+def sample(logits, out, temperature=None, top_p=None, seeds=None, positions=None, err=None):
     """One token per row of float ``logits`` [R, V]: greedy where temperature is 0
-    (or not given), else a draw from softmax(logits / temperature)."""
+    (or not given), else a draw from softmax(logits / temperature).  With ``err`` (the kernels'
+    error record) ``out`` has four more ints than rows, and the record is copied behind the tokens."""
     R, V = logits.shape
+    if err is not None:
+        if out.shape[0] != R + 4:
+            raise KernelError(f"sample: with an error record the output holds rows + 4 ints, got {out.shape[0]} for {R} rows")
+        if R == 0:
+            out.copy_(err)
+            return out
     _l.check(_l.load().dk_sample(_ptr(logits, "logits", torch.float32), logits.stride(0) if R else V, R, V,
                                  _ptr(temperature, "temperature", torch.float32), _ptr(top_p, "top_p", torch.float32),
                                  _ptr(seeds, "seeds", torch.int64), _ptr(positions, "positions", torch.int32),
-                                 _ptr(out, "out", torch.int32), _ptr(out_copy, "out_copy", torch.int32), _stream()), "sample")
+                                 _ptr(out, "out", torch.int32), _ptr(err, "err", torch.int32), _stream()), "sample")
     return out

@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import ops
 from ..parts import linear
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheSpec, StateSpec, TensorSpec
+from ..parts.base import BLOCKS, NORMS, CacheSpec, StateSpec, TensorSpec
 from .spec import ModelSpec, RunEntry
 
 
@@ -23,11 +23,7 @@ class Model:
         self.spec = spec
         self.blocks = []
         for ls in spec.layers:
-            norm1 = ls.norm1.build(NORMS)
-            mixer = ls.mixer.build(MIXERS)
-            norm2 = ls.norm2.build(NORMS)
-            ff = ls.feed_forward.build(FEED_FORWARDS)
-            self.blocks.append(BLOCKS.create(ls.block, norm1=norm1, mixer=mixer, norm2=norm2, feed_forward=ff))
+            self.blocks.append(BLOCKS.create(ls.block, parts={role: ps.build() for role, ps in ls.parts.items()}))
         self.final_norm = spec.final_norm.build(NORMS)
         self.embed_table = None
         self.lm_head = None
@@ -63,18 +59,20 @@ class Model:
         """cache index -> what its writer keeps per token (runs without a cache are left out)."""
         out = {}
         for e in self.order:
-            cs = self.blocks[e.layer].mixer.cache_spec()
+            cs = self.blocks[e.layer].cache_spec()
             if cs is None:
                 continue
             if e.writes_cache:
                 out[e.cache] = cs
         for e in self.order:
-            cs = self.blocks[e.layer].mixer.cache_spec()
-            if cs is not None and not e.writes_cache:
-                w = out[e.cache]
-                if (w.kv_heads, w.head_dim) != (cs.kv_heads, cs.head_dim):
-                    raise ValueError(f"layer {e.layer} reads cache {e.cache} whose head layout differs from its own")
+            cs = self.blocks[e.layer].cache_spec()
+            if cs is not None and not e.writes_cache and out[e.cache].layout != cs.layout:
+                raise ValueError(f"layer {e.layer} reads cache {e.cache} whose page layout differs from its own")
         return out
+
+    def decode_rows_differ(self) -> bool:
+        """True when some part treats decode rows otherwise than the same tokens in a prompt portion."""
+        return any(p.decode_rows_differ() for p in self.parts())
 
     def state_specs(self) -> Dict[str, StateSpec]:
         out: Dict[str, StateSpec] = {}
@@ -96,7 +94,7 @@ class Model:
         pending = None
         for e in self.order:
             block = self.blocks[e.layer]
-            cache = ctx.cache_view(e.cache, e.writes_cache) if block.mixer.cache_spec() is not None else None
+            cache = ctx.cache_view(e.cache, e.writes_cache) if block.cache_spec() is not None else None
             x, pending = block.forward(ctx, x, pending, cache)
             if ctx.capture is not None and ctx.capture.get("want_hidden"):
                 ctx.capture.setdefault("hidden", []).append((x.clone(), None if pending is None else pending.clone()))

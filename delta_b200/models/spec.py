@@ -2,18 +2,17 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import Mapping, Optional
 
 from ..parts.base import PartSpec, TensorSpec
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement around two norms, a mixer and a feed-forward."""
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    feed_forward: PartSpec
+    """One layer: a block arrangement and the parts it is built from, by the role each
+    plays in that block (the pre-norm block: norm1, mixer, norm2, feed_forward).  Every
+    ``PartSpec`` names its registry in ``category``."""
+    parts: Mapping[str, PartSpec]
     block: str = "pre_norm"
 
 
@@ -40,6 +39,7 @@ class ModelSpec:
     embedding: TensorSpec
     lm_head: TensorSpec
     max_positions: int = 0
+    ignorable_tensors: tuple = ()   # shell patterns of tensor names a model folder may hold beside the ones asked for
 
     def __post_init__(self):
         for e in self.order:

@@ -7,14 +7,18 @@ folder (``model.layers.N.self_attn.q_proj.weight`` and so on); the reference's
 own names (``layers.N.attention.wq.weight`` ...) belong to a converted
 checkpoint whose converter it does not ship.
 
-With a ``SelectiveCacheConfig`` each layer gets its DELTA role from
-``full_cache_layers`` (model.py:177-194).
+Options of the engine configuration that this builder reads: ``selective_cache`` (a
+``SelectiveCacheConfig``: each layer gets its DELTA role from ``full_cache_layers``,
+model.py:177-194) and ``rope_interleaved`` (the reference's pairing of rotary
+positions, for converted checkpoints).  Older exports store ``rotary_emb.inv_freq``
+buffers beside the weights; the loader is told that they may be there.
 """
 from __future__ import annotations
 
 from typing import Optional
 
-from ..config.engine_config import EngineConfig, SelectiveCacheConfig
+from ..config.engine_config import EngineConfig
+from ..config.selective_cache import SelectiveCacheConfig
 from ..config.model_config import YiConfig
 from ..parts.base import PartSpec, TensorSpec
 from .spec import LayerSpec, ModelSpec, RunEntry
@@ -22,11 +26,11 @@ from .spec import LayerSpec, ModelSpec, RunEntry
 
 def yi_spec(cfg: YiConfig, engine: Optional[EngineConfig] = None) -> ModelSpec:
     engine = engine or EngineConfig()
-    sel: Optional[SelectiveCacheConfig] = engine.selective
+    sel: Optional[SelectiveCacheConfig] = engine.option("selective_cache")
     d, hd = cfg.hidden_size, cfg.head_dim
     max_pos = max(cfg.max_position_embeddings, engine.max_seq_len)
     position = PartSpec("rotary", dict(head_dim=hd, theta=cfg.rope_theta, max_positions=max_pos,
-                                       interleaved=engine.rope_interleaved))
+                                       interleaved=bool(engine.option("rope_interleaved", False))), "position")
     layers = []
     for i in range(cfg.num_hidden_layers):
         pre = f"model.layers.{i}."
@@ -38,15 +42,15 @@ def yi_spec(cfg: YiConfig, engine: Optional[EngineConfig] = None) -> ModelSpec:
             if role != "full":
                 mixer.update(role=role, subset_cache_size=sel.subset_cache_size, keep_last=sel.keep_last,
                              compression_ratio=sel.compression_ratio, position_bias=sel.position_bias)
-        layers.append(LayerSpec(
-            norm1=PartSpec("rms_norm", dict(name=pre + "input_layernorm.weight", width=d, eps=cfg.rms_norm_eps)),
-            mixer=PartSpec("gqa_attention", mixer),
-            norm2=PartSpec("rms_norm", dict(name=pre + "post_attention_layernorm.weight", width=d, eps=cfg.rms_norm_eps)),
-            feed_forward=PartSpec("swiglu", dict(prefix=pre + "mlp.", width=d, intermediate=cfg.intermediate_size))))
+        layers.append(LayerSpec(dict(
+            norm1=PartSpec("rms_norm", dict(name=pre + "input_layernorm.weight", width=d, eps=cfg.rms_norm_eps), "norm"),
+            mixer=PartSpec("gqa_attention", mixer, "mixer"),
+            norm2=PartSpec("rms_norm", dict(name=pre + "post_attention_layernorm.weight", width=d, eps=cfg.rms_norm_eps), "norm"),
+            feed_forward=PartSpec("swiglu", dict(prefix=pre + "mlp.", width=d, intermediate=cfg.intermediate_size), "feed_forward"))))
     return ModelSpec(
         vocab_size=cfg.vocab_size, width=d, layers=tuple(layers),
         order=tuple(RunEntry(i) for i in range(cfg.num_hidden_layers)),
-        final_norm=PartSpec("rms_norm", dict(name="model.norm.weight", width=d, eps=cfg.rms_norm_eps)),
+        final_norm=PartSpec("rms_norm", dict(name="model.norm.weight", width=d, eps=cfg.rms_norm_eps), "norm"),
         embedding=TensorSpec("model.embed_tokens.weight", (cfg.vocab_size, d), kind="table"),
         lm_head=TensorSpec("lm_head.weight", (cfg.vocab_size, d), kind="matrix"),
-        max_positions=max_pos)
+        max_positions=max_pos, ignorable_tensors=("*.rotary_emb.inv_freq",))

@@ -14,7 +14,9 @@ every new token attends causally to the keys of its request
   "subset"   decode rows read only the chosen pages (backend.py:486-516); before a
              planner has run in a step these are the most recent pages
              (backend.py:1871-1873).
-Rows of a prompt always read everything.
+Rows of a prompt always read everything; the planner and subset roles apply to rows
+flagged ``ROW_DECODE`` (a single token at or after the prompt's end) of requests that hold
+more pages than the subset.  Which kernels run is chosen in ``attention_kernels``.
 """
 from __future__ import annotations
 
@@ -24,8 +26,8 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from . import linear
-from .base import MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, PartSpec, StateSpec, TensorSpec
+from . import attention_kernels, linear
+from .base import MIXERS, PAGE, POSITION_ENCODINGS, ROW_DECODE, CacheSpec, Mixer, PartSpec, StateSpec, TensorSpec
 
 SELECTED_PAGES = "delta.selected_pages"
 SELECTED_COUNT = "delta.selected_count"
@@ -71,7 +73,11 @@ class GQAAttention(Mixer):
         self.w_o = tensors[p + "o_proj.weight"]
 
     def cache_spec(self):
-        return CacheSpec(self.kv_heads, self.head_dim, self.window)
+        # a page of a layer: [K|V][kv head][offset in the page][head_dim]
+        return CacheSpec((2, self.kv_heads, PAGE, self.head_dim), self.window)
+
+    def decode_rows_differ(self):
+        return self.role != "full"
 
     def state_specs(self):
         if self.role == "full":
@@ -80,7 +86,7 @@ class GQAAttention(Mixer):
 
     # ---- a step ------------------------------------------------------------
     def begin_step(self, ctx):
-        if self.role == "full" or not ctx.any_selective or not ctx.once("delta.recent_pages"):
+        if self.role == "full" or not ctx.any_row_flag(ROW_DECODE) or not ctx.once("delta.recent_pages"):
             return
         ops.recent_pages(ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
                          ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), ctx.page_size, self.ratio)
@@ -91,27 +97,29 @@ class GQAAttention(Mixer):
         qkv = linear.linear(ctx, x, self.w_qkv)
         table = self.position.table(x.device) if self.position is not None else None
         interleaved = bool(getattr(self.position, "interleaved", False))
-        fuse = ctx.can_fuse_rope_append(H, KV, hd, cache.page_size, interleaved)
+        fuse = attention_kernels.can_fuse_rope_append(ctx, H, KV, hd, cache.page_size, interleaved)
         if not fuse:
-            ops.rope_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.kv if cache.writes else None, table,
+            ops.rope_append(qkv, ctx.tok_pos, ctx.tok_row, cache.block_table, cache.pages if cache.writes else None, table,
                             H, KV, hd, cache.page_size, interleaved, err=ctx.err)
         out = torch.empty((T, H * hd), dtype=x.dtype, device=x.device)
-        selective = self.role != "full" and ctx.any_selective
+        selective = self.role != "full" and ctx.any_row_flag(ROW_DECODE)
         dump = lse = None
+        widest = ctx.cache.max_pages_per_request
         if self.role == "planner" and selective:
-            dump = ctx.scratch("delta.dump", (ctx.num_rows, H, ctx.max_pages * cache.page_size), torch.float32)
-            lse = ctx.scratch("delta.lse", (T, H), torch.float32)
+            dump = ctx.scratch("delta.dump", (ctx.num_rows, H, ctx.max_pages * cache.page_size), torch.float32,
+                               bound=(ctx.max_rows, H, widest * cache.page_size))
+            lse = ctx.scratch("delta.lse", (T, H), torch.float32, bound=(ctx.max_step_tokens, H))
         params = ops.make_attn_params(
-            q=qkv, q_stride=qkv.shape[1], out=out, kv=cache.kv, block_table=cache.block_table, tok_row=ctx.tok_row,
+            q=qkv, q_stride=qkv.shape[1], out=out, kv=cache.pages, block_table=cache.block_table, tok_row=ctx.tok_row,
             tok_pos=ctx.tok_pos, H=H, KV=KV, hd=hd, ps=cache.page_size, scale=self.scale, row_slot=ctx.row_slot,
             row_flags=ctx.row_flags, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_pos_start=ctx.row_pos_start,
             sel_pages=ctx.state(SELECTED_PAGES) if (self.role == "subset" and selective) else None,
             sel_count=ctx.state(SELECTED_COUNT) if (self.role == "subset" and selective) else None,
             dump=dump, lse=lse, err=ctx.err, window=self.window or 0,
             fuse=(2 if cache.writes else 1) if fuse else 0, rope_table=table if fuse else None)
-        ctx.attention(params)
+        attention_kernels.run(ctx, params, cache.group)
         if self.role == "planner" and selective:
-            scores = ctx.scratch("delta.page_scores", (ctx.num_rows, ctx.max_pages), torch.float32)
+            scores = ctx.scratch("delta.page_scores", (ctx.num_rows, ctx.max_pages), torch.float32, bound=(ctx.max_rows, widest))
             ops.page_scores(dump, lse, ctx.row_flags, ctx.row_q_start, ctx.row_pos_start, ctx.row_q_len, scores,
                             cache.page_size, self.k, self.ratio)
             ops.select_pages(scores, ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
@@ -122,6 +130,6 @@ class GQAAttention(Mixer):
                 pages, counts = ctx.state(SELECTED_PAGES).cpu(), ctx.state(SELECTED_COUNT).cpu()
                 planned = ctx.capture.setdefault("planned", {})
                 for r in ctx.host["rows"]:
-                    if r.selective and int(counts[r.slot]) >= 0:
+                    if (r.flags & ROW_DECODE) and int(counts[r.slot]) >= 0:
                         planned[(self.prefix, r.slot, r.start_pos)] = pages[r.slot, :int(counts[r.slot])].tolist()
         return linear.linear(ctx, out, self.w_o)

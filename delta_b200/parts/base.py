@@ -37,14 +37,34 @@ class TensorSpec:
     init: str = "normal"
 
 
+PAGE = "page"     # the axis of a page layout that counts the tokens of the page
+
+
 @dataclass(frozen=True)
 class CacheSpec:
-    """Keys and values a mixer appends per token, and how far back it reads.
-    Mixers with equal specs share a cache group (one pool of pages, one block
-    table per request); ``window`` None means all keys are kept."""
-    kv_heads: int
-    head_dim: int
+    """What a mixer keeps per token, and how far back it reads.
+
+    ``layout`` is the shape of one page of one layer with the token axis written
+    as ``PAGE``: keys and values per head are ``(2, kv_heads, PAGE, head_dim)``, one
+    latent vector per token is ``(PAGE, width)``, keys and values of different
+    widths can be packed as ``(kv_heads, PAGE, k_width + v_width)``.  The cache
+    manager allocates ``[layers of the group, pages, *layout]`` with the page size
+    in place of ``PAGE`` and knows nothing else about the contents.  Mixers with
+    equal specs share a cache group (one pool of pages, one block table per
+    request); ``window`` None means every token is kept."""
+    layout: tuple
     window: Optional[int] = None
+
+    def __post_init__(self):
+        if tuple(self.layout).count(PAGE) != 1:
+            raise ValueError(f"a page layout names the token axis once, as PAGE: {self.layout}")
+        object.__setattr__(self, "layout", tuple(self.layout))
+
+    def page_shape(self, page_size: int) -> tuple:
+        return tuple(page_size if a == PAGE else int(a) for a in self.layout)
+
+    def describe(self) -> str:
+        return "x".join("P" if a == PAGE else str(a) for a in self.layout) + (f"w{self.window}" if self.window else "")
 
 
 @dataclass(frozen=True)
@@ -74,6 +94,12 @@ class Part:
 
     def begin_step(self, ctx) -> None:
         """Called once per step before any layer runs."""
+
+    def decode_rows_differ(self) -> bool:
+        """True when the part treats a row flagged ``ROW_DECODE`` otherwise than the same
+        token inside a prompt portion.  The scheduler then never folds generated tokens
+        into a prompt portion: a request that is recomputed feeds them one per step."""
+        return False
 
 
 class Norm(Part):
@@ -113,12 +139,41 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of norms, mixer and feed-forward around the residual stream.
-    ``forward(ctx, x, pending, cache)`` takes the stream x [T, d] and a not yet added
-    update ``pending`` (or None) and returns the same pair."""
+    """Arrangement of parts around the residual stream.  A block is built from a dict
+    of parts, ``{role: part}``; which roles it needs is the block's own business (the
+    pre-norm block: norm1, mixer, norm2, feed_forward; another block may take more
+    norms, no feed-forward, two mixers).  ``forward(ctx, x, pending, cache)`` takes the
+    stream x [T, d] and a not yet added update ``pending`` (or None) and returns the
+    same pair."""
+
+    roles: tuple = ()
+
+    def __init__(self, parts: Dict[str, Part]):
+        missing = [r for r in self.roles if r not in parts]
+        extra = [r for r in parts if r not in self.roles]
+        if missing or extra:
+            raise ValueError(f"{type(self).__name__} takes the parts {list(self.roles)}; missing {missing}, not taken {extra}")
+        self._parts = dict(parts)
+        for role, part in parts.items():
+            setattr(self, role, part)
+
+    def parts(self) -> list:
+        return list(self._parts.values())
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        """What a run of this block appends to its cache: that of its first part that keeps one."""
+        for p in self._parts.values():
+            cs = p.cache_spec() if hasattr(p, "cache_spec") else None
+            if cs is not None:
+                return cs
+        return None
 
     def forward(self, ctx, x, pending, cache):
         raise NotImplementedError
+
+
+# Flags of a row of a step (``RowInput.flags``, ``ctx.row_flags``), for parts to interpret.
+ROW_DECODE = 1      # a single token at or after the end of the request's prompt
 
 
 # -------------------------------------------------------------- registries
@@ -158,11 +213,21 @@ FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
 
 
+REGISTRIES = {"norm": NORMS, "position": POSITION_ENCODINGS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
+              "block": BLOCKS}
+
+
 @dataclass(frozen=True)
 class PartSpec:
-    """Registry name of a part and its parameters."""
+    """Registry name of a part, its parameters, and the registry it is looked up in
+    ("norm", "position", "mixer", "feed_forward", "block")."""
     kind: str
     params: dict = field(default_factory=dict)
+    category: str = ""
 
-    def build(self, registry: Registry, **extra):
+    def build(self, registry: Optional[Registry] = None, **extra):
+        if registry is None:
+            if self.category not in REGISTRIES:
+                raise KeyError(f"part '{self.kind}' names no registry (category '{self.category}'); known: {', '.join(REGISTRIES)}")
+            registry = REGISTRIES[self.category]
         return registry.create(self.kind, **{**self.params, **extra})

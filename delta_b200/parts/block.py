@@ -12,11 +12,7 @@ from .base import BLOCKS, Block
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
-    def __init__(self, norm1, mixer, norm2, feed_forward):
-        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
-
-    def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.feed_forward]
+    roles = ("norm1", "mixer", "norm2", "feed_forward")
 
     def forward(self, ctx, x, pending, cache):
         a = self.norm1.forward(ctx, x, add=pending)

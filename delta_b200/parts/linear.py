@@ -139,11 +139,35 @@ def choices() -> Dict[tuple, str]:
     return dict(_choice)
 
 
+def save_choices(path) -> None:
+    """Writes what the measurements chose (and the times they saw) as JSON, so that a later
+    run starts without measuring and takes the same kernels (the same bfloat16 bits)."""
+    import json
+    items = [dict(rows=k[0], n=k[1], k=k[2], swiglu=bool(k[3]), out=str(k[4]).replace("torch.", ""), kernel=v,
+                  times_us=_times.get((k[0], k[1], k[2], k[3]), {})) for k, v in sorted(_choice.items(), key=str)]
+    with open(path, "w") as f:
+        json.dump({"product_kernels": items}, f, indent=1)
+
+
+def load_choices(path) -> int:
+    """Takes the choices of a file written by ``save_choices``; returns how many it held.  A
+    kernel name that this build does not know is an error, not a silent new measurement."""
+    import json
+    with open(path) as f:
+        items = json.load(f)["product_kernels"]
+    known = {"small", "lib", "sk", "none", "tc1", "tc2", "tc4", "tc8"}
+    for it in items:
+        if it["kernel"] not in known:
+            raise ValueError(f"{path}: unknown product kernel '{it['kernel']}'")
+        _choice[(int(it["rows"]), int(it["n"]), int(it["k"]), bool(it["swiglu"]), getattr(torch, it["out"]))] = it["kernel"]
+    return len(items)
+
+
 def swiglu_linear(ctx, x: torch.Tensor, w_gate_up: torch.Tensor):
     """silu(x gate^T) * (x up^T) with the gate fused into the product's epilogue when the batch
     is small enough for the streaming kernels; else None."""
     T = x.shape[0]
-    if x.dtype != torch.bfloat16 or ctx.plain_products or not (0 < T <= SMALL_M):
+    if x.dtype != torch.bfloat16 or ("products" in ctx.plain_kernels) or not (0 < T <= SMALL_M):
         return None
     kind = choose(T, w_gate_up, x, True, x.dtype, ctx.err)
     if kind == "none":
@@ -157,7 +181,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tenso
     """x [T, K], w [N, K] -> [T, N] in ``out_dtype`` (the type of x by default)."""
     out_dtype = out_dtype or x.dtype
     T, N = x.shape[0], w.shape[0]
-    if x.dtype == torch.float32 or ctx.plain_products:
+    if x.dtype == torch.float32 or ("products" in ctx.plain_kernels):
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
         if T:
             ops.gemm_nt_plain(x, w, out)

@@ -1,1 +1,1 @@
-from .sampler import SamplingParams, sample, uniform_of
+from .sampler import SamplingParams, uniform_of

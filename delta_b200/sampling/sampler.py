@@ -7,16 +7,12 @@ probabilities, then ``softmax(logits / T)`` and one multinomial draw) give the
 meaning of the other two options here.  The draw uses a counter-based generator
 keyed by (seed of the request, position of the new token), so what a request
 samples depends neither on its batch nor on how its prompt was cut into steps.
+The kernel (csrc/sampling.cu) is launched by the step function with the rows'
+parameters from the step's staging block.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional
-
-import numpy as np
-import torch
-
-from ..kernels import ops
 
 _MASK = (1 << 64) - 1
 
@@ -42,22 +38,3 @@ def uniform_of(seed: int, position: int) -> float:
     z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
     z ^= z >> 31
     return ((z >> 40) + 0.5) / 16777216.0
-
-
-def sample(logits: torch.Tensor, params: List[SamplingParams], positions: List[int]) -> torch.Tensor:
-    """One token id per row of float32 ``logits`` [R, V] (device int32 tensor).
-    ``positions[r]`` is the position the new token of row r will take."""
-    R = logits.shape[0]
-    out = torch.empty(R, dtype=torch.int32, device=logits.device)
-    if R == 0:
-        return out
-    if all(p.temperature == 0 for p in params):
-        return ops.sample(logits, out)
-    dev = logits.device
-    temp = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(dev, non_blocking=True)
-    top_p = None
-    if any(p.top_p < 1.0 for p in params):
-        top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32).to(dev, non_blocking=True)
-    seeds = torch.from_numpy(np.array([p.seed & _MASK for p in params], dtype=np.uint64).view(np.int64)).to(dev, non_blocking=True)
-    pos = torch.tensor(positions, dtype=torch.int32).to(dev, non_blocking=True)
-    return ops.sample(logits, out, temperature=temp, top_p=top_p, seeds=seeds, positions=pos)

@@ -3,7 +3,9 @@
 The reference loads a pickled state dict strictly (DELTA/Engine/utils.py:209-231)
 and casts everything to bfloat16 (line 230).  Here tensors are looked up by their
 names in the model folder; every problem (missing names, names nobody asked for,
-wrong shapes) is collected and raised as one error.
+wrong shapes) is collected and raised as one error.  An architecture may name
+patterns of tensors that a folder is allowed to hold although the model does not
+read them (stored ``rotary_emb.inv_freq`` buffers of older exports, for one).
 
 Types: operands of matrix products and the embedding table are kept in the
 compute type (bfloat16, or float32 on the 32-bit path); integer tables become
@@ -11,8 +13,9 @@ int32; any other tensor that the file stores in 32 bit stays in 32 bit.
 """
 from __future__ import annotations
 
+from fnmatch import fnmatchcase
 from pathlib import Path
-from typing import Dict, List
+from typing import Dict, List, Sequence
 
 import torch
 
@@ -47,7 +50,8 @@ def target_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) ->
     return torch.float32 if stored in (torch.float32, torch.float64) else compute
 
 
-def load_tensors(folder, specs: List[TensorSpec], compute: torch.dtype, device) -> Dict[str, torch.Tensor]:
+def load_tensors(folder, specs: List[TensorSpec], compute: torch.dtype, device, ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
+    """``ignorable``: shell patterns of names that may be in the folder without being asked for."""
     files = open_model_files(folder)
     where = {}
     for f in files:
@@ -55,7 +59,7 @@ def load_tensors(folder, specs: List[TensorSpec], compute: torch.dtype, device) 
             where[n] = f
     wanted = {s.name: s for s in specs}
     missing = [n for n in wanted if n not in where]
-    unexpected = sorted(n for n in where if n not in wanted)
+    unexpected = sorted(n for n in where if n not in wanted and not any(fnmatchcase(n, pat) for pat in ignorable))
     wrong_shape, wrong_type = [], []
     for n, s in wanted.items():
         if n in where:

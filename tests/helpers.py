@@ -111,12 +111,13 @@ def mixed(lengths, prompt_lens, seed=0, max_live=4, portion_sizes=(5, 2, 11, 3, 
 
 # ---- running a schedule through the engine's step function -----------------------
 
-def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, selective=False, planned=None):
+def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, planned=None):
     """Feeds the schedule through ``runner`` (a ModelRunner) and returns
     {(request, position): logits row (CPU float32)}.  Logits are asked for at every
-    token.  With ``selective`` the single tokens at or after a request's prompt
-    length are decode tokens that page selection applies to."""
+    token.  With ``prompt_lens`` the single tokens at or after a request's prompt
+    length are flagged as decode rows (page selection applies to those)."""
     from delta_b200.engine.step import RowInput
+    from delta_b200.parts.base import ROW_DECODE
     slots = {}
     out = {}
     if planned is not None:
@@ -126,8 +127,9 @@ def run_schedule(runner, token_lists, steps, ends=None, prompt_lens=None, select
         for (i, start, count) in step:
             if i not in slots:
                 slots[i] = runner.cache.acquire_slot()
-            sel = bool(selective and count == 1 and prompt_lens is not None and start >= prompt_lens[i])
-            rows.append(RowInput(slots[i], token_lists[i][start:start + count], start, list(range(count)), selective=sel))
+            dec = bool(count == 1 and prompt_lens is not None and start >= prompt_lens[i])
+            rows.append(RowInput(slots[i], token_lists[i][start:start + count], start, list(range(count)),
+                                 flags=ROW_DECODE if dec else 0))
             keys.extend((i, start + j) for j in range(count))
         logits = runner.run_rows(rows).float().cpu()
         assert logits.shape[0] == len(keys)

@@ -6,14 +6,14 @@ import torch
 
 from delta_b200.cache import CacheManager, OutOfPages, PagePool
 from delta_b200.engine.scheduler import FAILED, FINISHED, RUNNING, WAITING, Scheduler
-from delta_b200.parts.base import CacheSpec, StateSpec
+from delta_b200.parts.base import PAGE, CacheSpec, StateSpec
 from delta_b200.sampling import SamplingParams
 
 
 def manager(num_pages=16, page_size=4, max_slots=4, max_seq_len=64, window=None, states=None):
-    specs = {0: CacheSpec(2, 8), 1: CacheSpec(2, 8)}
+    specs = {0: CacheSpec((2, 2, PAGE, 8)), 1: CacheSpec((2, 2, PAGE, 8))}
     if window:
-        specs[2] = CacheSpec(2, 8, window)
+        specs[2] = CacheSpec((2, 2, PAGE, 8), window)
     return CacheManager(specs, states or {}, max_slots=max_slots, max_seq_len=max_seq_len, page_size=page_size,
                         num_pages=num_pages, dtype=torch.float32, device="cpu")
 
@@ -40,19 +40,19 @@ def test_grow_release_reuse():
     m = manager(num_pages=6)
     s = m.acquire_slot()
     m.grow(s, 9)                      # 3 pages of 4 tokens
-    assert m.pages_in_use() == {"kv2x8": 3}
+    assert m.pages_in_use() == {"2x2xPx8": 3}
     m.grow(s, 12)
-    assert m.pages_in_use() == {"kv2x8": 3}     # no page in advance at a page's edge
+    assert m.pages_in_use() == {"2x2xPx8": 3}     # no page in advance at a page's edge
     m.grow(s, 13)
-    assert m.pages_in_use() == {"kv2x8": 4}
+    assert m.pages_in_use() == {"2x2xPx8": 4}
     t = m.acquire_slot()
     with pytest.raises(OutOfPages):
         m.grow(t, 12)
-    assert m.pages_in_use() == {"kv2x8": 4}     # all or nothing
-    held = m.groups["kv2x8"].held(s)
+    assert m.pages_in_use() == {"2x2xPx8": 4}     # all or nothing
+    held = m.groups["2x2xPx8"].held(s)
     m.release_slot(s)
     m.grow(t, 16)
-    assert set(m.groups["kv2x8"].held(t)) == set(held)   # pages are used again
+    assert set(m.groups["2x2xPx8"].held(t)) == set(held)   # pages are used again
     with pytest.raises(ValueError, match="twice"):
         m.release_slot(s)
     m.check()
@@ -60,23 +60,23 @@ def test_grow_release_reuse():
 
 def test_layers_share_a_group_and_windows_have_their_own():
     m = manager(window=6)
-    assert set(m.groups) == {"kv2x8", "kv2x8w6"}
-    assert m.groups["kv2x8"].cache_ids == [0, 1] and m.groups["kv2x8w6"].cache_ids == [2]
-    assert m.layer_kv(1).shape == (16 + 1, 2, 2, 4, 8)      # the pool's 16 pages and the padding slot's spare page
+    assert set(m.groups) == {"2x2xPx8", "2x2xPx8w6"}
+    assert m.groups["2x2xPx8"].cache_ids == [0, 1] and m.groups["2x2xPx8w6"].cache_ids == [2]
+    assert m.layer_pages(1).shape == (16 + 1, 2, 2, 4, 8)      # the pool's 16 pages and the padding slot's spare page
     s = m.acquire_slot()
     for n in range(1, 41):
         m.grow(s, n)
         m.advance(s, n)
         m.check()
-        g = m.groups["kv2x8w6"]
+        g = m.groups["2x2xPx8w6"]
         # the next query (position n) reads keys n-5 .. n; earlier pages are given back
         first_needed = max(0, n - 6 + 1) // 4
         assert int(g.first_page[s]) == first_needed
         assert len(g.held(s)) == (n + 3) // 4 - first_needed
-        assert len(m.groups["kv2x8"].held(s)) == (n + 3) // 4
-    assert m.groups["kv2x8w6"].pool.held_pages <= 3
+        assert len(m.groups["2x2xPx8"].held(s)) == (n + 3) // 4
+    assert m.groups["2x2xPx8w6"].pool.held_pages <= 3
     m.release_slot(s)
-    assert m.pages_in_use() == {"kv2x8": 0, "kv2x8w6": 0}
+    assert m.pages_in_use() == {"2x2xPx8": 0, "2x2xPx8w6": 0}
 
 
 def test_the_padding_slot_holds_the_spare_page_and_no_pool_page():
@@ -204,6 +204,66 @@ def test_out_of_pages_preempts_the_youngest_and_recomputes():
     again = [row for step in log for row in step if row[0] == 1 and row[1] == 0]
     assert len(again) == 2 and again[1][2] > 11
     assert all(v == 0 for v in m.pages_in_use().values())
+
+
+def test_recomputing_after_a_preemption_keeps_decode_positions_single():
+    """When some part treats decode rows in a way of its own, a preempted request runs its prompt
+    in portions again and every token it had generated as a decode row of its own, unsampled,
+    until it is where it was."""
+    m = manager(num_pages=7, page_size=4, max_slots=4, max_seq_len=28)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=64, decode_singly=True)
+    a = sch.add_request(list(range(11)), 24)
+    b = sch.add_request(list(range(11)), 24)
+    log = drive(sch, next_token=lambda r: 100 + len(r.output))
+    assert a.status == FINISHED and b.status == FINISHED and b.preemptions >= 1
+    assert a.output == [100 + i for i in range(13)] and b.output == [100 + i for i in range(13)]
+    rows_b = [row for step in log for row in step if row[0] == 1]
+    # no portion of b ever reaches past its prompt, and positions from the prompt's end on are single decode rows
+    for (_, start, count, samples, decode) in rows_b:
+        assert start + count <= 11 or (count == 1 and decode)
+    again = [row for row in rows_b if row[4] and not row[3]]
+    assert again and all(11 <= start < 11 + 13 for (_, start, *_rest) in again)
+    # a position that is computed again is not sampled again
+    sampled = [start for (_, start, count, samples, _d) in rows_b if samples]
+    assert len(sampled) == len(set(sampled)) == 13
+    assert all(v == 0 for v in m.pages_in_use().values())
+
+
+def test_prompts_first_does_not_hold_decoding_for_a_request_that_cannot_be_admitted():
+    """More requests than slots with prompts first: the waiting ones cannot be admitted until a
+    running one ends, so the running ones must go on decoding."""
+    m = manager(num_pages=64, page_size=4, max_slots=2, max_seq_len=32)
+    sch = Scheduler(m, max_batch=2, max_tokens_per_step=16)
+    sch.decode_while_prefill = False
+    reqs = [sch.add_request(list(range(5)), 9) for _ in range(5)]
+    drive(sch, max_steps=200)
+    assert all(r.status == FINISHED and len(r.output) == 4 for r in reqs)
+    # the same when the pool, not the slots, keeps the third request waiting
+    m = manager(num_pages=6, page_size=4, max_slots=4, max_seq_len=32)
+    sch = Scheduler(m, max_batch=4, max_tokens_per_step=16)
+    sch.decode_while_prefill = False
+    reqs = [sch.add_request(list(range(7)), 12) for _ in range(3)]
+    drive(sch, max_steps=200)
+    assert all(r.status == FINISHED for r in reqs)
+
+
+def test_a_cache_group_takes_any_page_layout():
+    """The manager allocates what the mixer declares: keys and values per head, one vector per
+    token, or keys and values of different widths packed side by side."""
+    specs = {0: CacheSpec((2, 2, PAGE, 8)), 1: CacheSpec((PAGE, 24)), 2: CacheSpec((3, PAGE, 16 + 40)), 3: CacheSpec((PAGE, 24))}
+    m = CacheManager(specs, {}, max_slots=2, max_seq_len=32, page_size=4, num_pages=9, dtype=torch.float32, device="cpu")
+    assert set(m.groups) == {"2x2xPx8", "Px24", "3xPx56"}
+    assert m.layer_pages(0).shape == (10, 2, 2, 4, 8) and m.layer_pages(1).shape == (10, 4, 24)
+    assert m.layer_pages(2).shape == (10, 3, 4, 56) and m.groups["Px24"].cache_ids == [1, 3]
+    s = m.acquire_slot()
+    m.grow(s, 9)
+    assert m.pages_in_use() == {"2x2xPx8": 3, "Px24": 3, "3xPx56": 3}
+    m.release_slot(s)
+    m.check()
+    with pytest.raises(ValueError):
+        CacheSpec((2, 4, 8))            # no token axis
+    with pytest.raises(ValueError):
+        CacheSpec((PAGE, 4, PAGE))      # two of them
 
 
 def test_a_request_that_can_never_fit_fails_at_once():

@@ -114,6 +114,27 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         "model.layers.1.mlp.up_proj.weight", "model.norm.weight"}
 
 
+def test_names_the_architecture_calls_ignorable_may_be_in_the_folder(tmp_path):
+    """Older exports store ``rotary_emb.inv_freq`` buffers beside the weights: the Yi specification
+    names them ignorable, so such a folder loads; any other name nobody asked for is still an error."""
+    folder = helpers.make_model_folder(tmp_path, "A", torch.float32)
+    tensors = read_safetensors_plain(folder / "model.safetensors")
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_safetensors(folder / "model.safetensors", tensors)
+    arch, cfg = read_config(folder)
+    spec = arch.build_spec(cfg, None)
+    specs = Model(spec).tensor_specs()
+    assert spec.ignorable_tensors
+    t = load_tensors(folder, specs, torch.float32, "cpu", ignorable=spec.ignorable_tensors)
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" not in t and len(t) == len(specs)
+    tensors["model.layers.0.self_attn.something_else"] = torch.zeros(8)
+    write_safetensors(folder / "model.safetensors", tensors)
+    with pytest.raises(WeightError) as e:
+        load_tensors(folder, specs, torch.float32, "cpu", ignorable=spec.ignorable_tensors)
+    assert e.value.unexpected == ["model.layers.0.self_attn.something_else"]
+
+
 def test_engine_config_checks():
     with pytest.raises(ValueError):
         EngineConfig(dtype="float16")
@@ -125,9 +146,9 @@ def test_engine_config_checks():
 def test_spec_follows_config_layer_by_layer():
     cfg = YiConfig.from_dict(helpers.tiny_config("C"))
     sel = SelectiveCacheConfig(full_cache_layers=(0,), subset_cache_size=3)
-    spec = yi_spec(cfg, EngineConfig(selective=sel))
-    roles = [l.mixer.params.get("role", "full") for l in spec.layers]
-    windows = [l.mixer.params["window"] for l in spec.layers]
+    spec = yi_spec(cfg, EngineConfig(options=dict(selective_cache=sel)))
+    roles = [l.parts["mixer"].params.get("role", "full") for l in spec.layers]
+    windows = [l.parts["mixer"].params["window"] for l in spec.layers]
     assert windows == [None, 24, None, 24]
     assert roles == ["planner", "full", "subset", "full"]   # windowed layers take no page selection
     m = Model(spec)

@@ -1,7 +1,9 @@
 """Each part of a layer alone against the plain functions, and toy parts that are defined
-here: a mixer with state of its own, a feed-forward with routing, another position encoding,
-a run order that names a layer twice and lets a run read another run's cache.  The toy parts
-are registered, built from a config.json and stepped without a change to the package."""
+here: a mixer with state of its own, a mixer whose cache holds one vector per token, a
+feed-forward with routing, another position encoding, a block with a norm more than the
+pre-norm block has, a run order that names a layer twice and lets a run read another run's
+cache.  The toy parts are registered, built from a config.json and stepped without a change
+to the package."""
 import json
 import math
 from dataclasses import dataclass
@@ -110,8 +112,8 @@ def test_rotary_table_and_both_pairings():
 def register_toys():
     from delta_b200.config.registry import register_architecture
     from delta_b200.models.spec import LayerSpec, ModelSpec, RunEntry
-    from delta_b200.parts.base import (FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, FeedForward, Mixer, PartSpec,
-                                       PositionEncoding, StateSpec, TensorSpec)
+    from delta_b200.parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, PAGE, POSITION_ENCODINGS, Block, CacheSpec, FeedForward,
+                                       Mixer, PartSpec, PositionEncoding, StateSpec, TensorSpec)
 
     if "toy_running_mean" not in MIXERS:
         @MIXERS.register("toy_running_mean")
@@ -143,6 +145,55 @@ def register_toys():
                         ys[q0 + i] = s
                     state[row.slot] = s
                 return (ys @ self.w_out.float().T).to(x.dtype)
+
+    if "toy_latent_memory" not in MIXERS:
+        @MIXERS.register("toy_latent_memory")
+        class LatentMemory(Mixer):
+            """Keeps one latent vector per token in its pages, c_t = x_t Wc^T, and gives
+            y_t = mean(c_0 .. c_t) Wo^T.  Its page layout has no heads and no key/value pair."""
+
+            def __init__(self, prefix, width, latent):
+                self.prefix, self.width, self.latent = prefix, width, latent
+
+            def tensor_specs(self):
+                return [TensorSpec(self.prefix + "down.weight", (self.latent, self.width)),
+                        TensorSpec(self.prefix + "up.weight", (self.width, self.latent))]
+
+            def bind(self, tensors):
+                self.w_down, self.w_up = tensors[self.prefix + "down.weight"], tensors[self.prefix + "up.weight"]
+
+            def cache_spec(self):
+                return CacheSpec((PAGE, self.latent))
+
+            def forward(self, ctx, x, cache):
+                assert tuple(cache.pages.shape[1:]) == (cache.page_size, self.latent)
+                c = x.float() @ self.w_down.float().T
+                ys = torch.empty((x.shape[0], self.latent), dtype=torch.float32, device=x.device)
+                ps = cache.page_size
+                for b, (row, q0, n) in enumerate(zip(ctx.host["rows"], ctx.host["q_start"], ctx.host["q_lens"])):
+                    table = cache.block_table[b]
+                    for i in range(n):
+                        pos = row.start_pos + i
+                        cache.pages[table[pos // ps], pos % ps] = c[q0 + i].to(cache.pages.dtype)
+                    held = torch.cat([cache.pages[table[j]] for j in range((row.start_pos + n + ps - 1) // ps)]).float()
+                    sums = held[:row.start_pos + n].cumsum(0)
+                    for i in range(n):
+                        pos = row.start_pos + i
+                        ys[q0 + i] = sums[pos] / (pos + 1)
+                return (ys @ self.w_up.float().T).to(x.dtype)
+
+    if "toy_sandwich" not in BLOCKS:
+        @BLOCKS.register("toy_sandwich")
+        class Sandwich(Block):
+            """h = x + post_norm(mixer(norm1(x))); out = h + feed_forward(norm2(h)): one norm more
+            than the pre-norm block."""
+            roles = ("norm1", "mixer", "post_norm", "norm2", "feed_forward")
+
+            def forward(self, ctx, x, pending, cache):
+                a = self.norm1.forward(ctx, x, add=pending)
+                y = self.post_norm.forward(ctx, self.mixer.forward(ctx, a, cache))
+                f = self.norm2.forward(ctx, x, add=y)
+                return x, self.feed_forward.forward(ctx, f)
 
     if "toy_routed" not in FEED_FORWARDS:
         @FEED_FORWARDS.register("toy_routed")
@@ -207,28 +258,39 @@ def register_toys():
         theta: float
         experts: int
         max_position_embeddings: int
+        latent: int
 
         @staticmethod
         def from_dict(c):
             return ToyConfig(c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
                              c["intermediate_size"], c["vocab_size"], c["rms_norm_eps"], c["rope_theta"], c["experts"],
-                             c["max_position_embeddings"])
+                             c["max_position_embeddings"], c["latent"])
 
     def toy_spec(cfg, engine):
         d = cfg.hidden_size
 
         def norm(name):
-            return PartSpec("rms_norm", dict(name=name, width=d, eps=cfg.eps))
-        pos = PartSpec("toy_partial_rotary", dict(head_dim=cfg.head_dim, theta=cfg.theta, max_positions=cfg.max_position_embeddings))
-        l0 = LayerSpec(norm("toy.0.n1"), PartSpec("gqa_attention", dict(prefix="toy.0.attn.", width=d, heads=cfg.heads,
-                                                                       kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, position=pos)),
-                       norm("toy.0.n2"), PartSpec("swiglu", dict(prefix="toy.0.mlp.", width=d, intermediate=cfg.intermediate_size)))
-        l1 = LayerSpec(norm("toy.1.n1"), PartSpec("toy_running_mean", dict(prefix="toy.1.mean.", width=d)),
-                       norm("toy.1.n2"), PartSpec("toy_routed", dict(prefix="toy.1.ff.", width=d, intermediate=cfg.intermediate_size,
-                                                                    experts=cfg.experts)))
+            return PartSpec("rms_norm", dict(name=name, width=d, eps=cfg.eps), "norm")
+        pos = PartSpec("toy_partial_rotary", dict(head_dim=cfg.head_dim, theta=cfg.theta, max_positions=cfg.max_position_embeddings),
+                       "position")
+        l0 = LayerSpec(dict(norm1=norm("toy.0.n1"),
+                            mixer=PartSpec("gqa_attention", dict(prefix="toy.0.attn.", width=d, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                                                                 head_dim=cfg.head_dim, position=pos), "mixer"),
+                            norm2=norm("toy.0.n2"),
+                            feed_forward=PartSpec("swiglu", dict(prefix="toy.0.mlp.", width=d, intermediate=cfg.intermediate_size),
+                                                  "feed_forward")))
+        l1 = LayerSpec(dict(norm1=norm("toy.1.n1"), mixer=PartSpec("toy_running_mean", dict(prefix="toy.1.mean.", width=d), "mixer"),
+                            norm2=norm("toy.1.n2"),
+                            feed_forward=PartSpec("toy_routed", dict(prefix="toy.1.ff.", width=d, intermediate=cfg.intermediate_size,
+                                                                     experts=cfg.experts), "feed_forward")))
+        l2 = LayerSpec(dict(norm1=norm("toy.2.n1"),
+                            mixer=PartSpec("toy_latent_memory", dict(prefix="toy.2.mem.", width=d, latent=cfg.latent), "mixer"),
+                            post_norm=norm("toy.2.post"), norm2=norm("toy.2.n2"),
+                            feed_forward=PartSpec("swiglu", dict(prefix="toy.2.mlp.", width=d, intermediate=cfg.intermediate_size),
+                                                  "feed_forward")), block="toy_sandwich")
         # layer 0 runs three times: with its own cache, again with another cache, and reading the first run's cache
-        order = (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(0, cache=0, writes_cache=False))
-        return ModelSpec(vocab_size=cfg.vocab_size, width=d, layers=(l0, l1), order=order, final_norm=norm("toy.norm"),
+        order = (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(0, cache=0, writes_cache=False), RunEntry(2))
+        return ModelSpec(vocab_size=cfg.vocab_size, width=d, layers=(l0, l1, l2), order=order, final_norm=norm("toy.norm"),
                          embedding=TensorSpec("toy.embed", (cfg.vocab_size, d), kind="table"),
                          lm_head=TensorSpec("toy.head", (cfg.vocab_size, d)), max_positions=cfg.max_position_embeddings)
 
@@ -237,7 +299,7 @@ def register_toys():
 
 TOY = dict(architectures=["ToyForCausalLM"], hidden_size=48, num_attention_heads=3, num_key_value_heads=1, head_dim=16,
            intermediate_size=80, vocab_size=100, rms_norm_eps=1e-5, rope_theta=10000.0, experts=3,
-           max_position_embeddings=128)
+           max_position_embeddings=128, latent=24)
 
 
 def toy_plain(folder, tokens):
@@ -285,18 +347,28 @@ def toy_plain(folder, tokens):
             out[m] = torch.nn.functional.gelu(f[m] @ w[f"toy.1.ff.experts.{e}.up.weight"].T) @ w[f"toy.1.ff.experts.{e}.down.weight"].T
         return h + out
 
+    def memory_layer(x):
+        a = P.rms_norm(x, w["toy.2.n1"], c["rms_norm_eps"])
+        lat = a @ w["toy.2.mem.down.weight"].T
+        means = lat.cumsum(0) / torch.arange(1, T + 1)[:, None]
+        h = x + P.rms_norm(means @ w["toy.2.mem.up.weight"].T, w["toy.2.post"], c["rms_norm_eps"])
+        f = P.rms_norm(h, w["toy.2.n2"], c["rms_norm_eps"])
+        return h + P.swiglu(f, w["toy.2.mlp.gate_proj.weight"], w["toy.2.mlp.up_proj.weight"], w["toy.2.mlp.down_proj.weight"])
+
     x = w["toy.embed"][torch.tensor(tokens)]
     x, kv0 = attn_layer(x)
     x = mean_layer(x)
     x, _ = attn_layer(x)
     x, _ = attn_layer(x, kv_from=kv0)
+    x = memory_layer(x)
     return P.rms_norm(x, w["toy.norm"], c["rms_norm_eps"]) @ w["toy.head"].T
 
 
 def test_toy_parts_are_registered_built_and_stepped(tmp_path):
-    """A mixer with state of its own, a routed feed-forward, another position encoding and a run
-    order with a repeated layer and a shared cache: built from a model folder and stepped whole,
-    token by token, in portions and mixed, with the same logits every time."""
+    """A mixer with state of its own, one whose pages hold a latent vector per token, a routed
+    feed-forward, another position encoding, a block with an extra norm and a run order with a
+    repeated layer and a shared cache: built from a model folder and stepped whole, token by
+    token, in portions and mixed, with the same logits every time."""
     from delta_b200.config import EngineConfig
     from delta_b200.config.registry import unregister_architecture
     from delta_b200.engine.step import ModelRunner
@@ -308,7 +380,9 @@ def test_toy_parts_are_registered_built_and_stepped(tmp_path):
         toks = [helpers.random_tokens(n, TOY["vocab_size"], 200 + i) for i, n in enumerate(lengths)]
         refs = [toy_plain(folder, t) for t in toks]
         r = ModelRunner(folder, engine_config=EngineConfig(max_batch=4, max_seq_len=64, page_size=8, num_pages=40, dtype="float32"))
-        assert set(r.cache.groups) == {"kv1x16"} and r.cache.groups["kv1x16"].cache_ids == [0, 2]
+        assert set(r.cache.groups) == {"2x1xPx16", "Px24"} and r.cache.groups["2x1xPx16"].cache_ids == [0, 2]
+        assert r.cache.groups["Px24"].cache_ids == [4] and r.cache.groups["Px24"].pages.shape == (1, 40 + 1, 8, 24)
+        assert [type(b).__name__ for b in r.model.blocks] == ["PreNormBlock", "PreNormBlock", "Sandwich"]
         assert r.cache.states["toy.1.mean.state"].shape == (4 + 1, 48)     # four requests and the padding slot
         prompt_lens = [n // 2 for n in lengths]
         mixed, ends = helpers.mixed(lengths, prompt_lens, seed=2)

@@ -33,16 +33,16 @@ def compare(results, refs, lengths, what):
 
 def test_real_widths_fast_kernels_against_plain_kernels(monkeypatch):
     from delta_b200.config import EngineConfig
-    from delta_b200.engine import attention_dispatch
+    from delta_b200.parts import attention_kernels
     from delta_b200.engine.step import ModelRunner
-    monkeypatch.setattr(attention_dispatch, "TMA_MIN_TILES", 1)    # short blocks too take the TMA variant here
+    monkeypatch.setattr(attention_kernels, "TMA_MIN_TILES", 1)    # short blocks too take the TMA variant here
     lengths = [700, 300, 1100]
     toks = [helpers.random_tokens(n, CFG["vocab_size"], 500 + i) for i, n in enumerate(lengths)]
 
     def runner(plain):
         r = ModelRunner(None, engine_config=EngineConfig(max_batch=4, max_seq_len=1152, page_size=16, dtype="bfloat16"),
                         config_json=CFG, seed=3)
-        r.plain_products = r.plain_attention = plain
+        r.plain_kernels = {"products", "attention"} if plain else set()
         return r
 
     slow = runner(True)

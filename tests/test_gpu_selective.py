@@ -50,7 +50,7 @@ def test_selective_cache(model_folders, which, full, k, L, ratio, dtype):
     assert want, "the case never selected anything"
 
     def runner(num_pages):
-        cfg = EngineConfig(max_batch=4, max_seq_len=256, page_size=ps, num_pages=num_pages, dtype=dtype, selective=sel)
+        cfg = EngineConfig(max_batch=4, max_seq_len=256, page_size=ps, num_pages=num_pages, dtype=dtype, options=dict(selective_cache=sel))
         return ModelRunner(folder, engine_config=cfg)
 
     def check(res, got, what):
@@ -70,14 +70,14 @@ def test_selective_cache(model_folders, which, full, k, L, ratio, dtype):
         steps.append([(i, 0, pl)])
         steps.extend([[(i, p, 1)] for p in range(pl, n)])
     got = {}
-    res = helpers.run_schedule(runner(4 * (256 // ps)), toks, steps, prompt_lens=prompt_lens, selective=True, planned=got)
+    res = helpers.run_schedule(runner(4 * (256 // ps)), toks, steps, prompt_lens=prompt_lens, planned=got)
     check(res, got, "alone")
 
     # prompts in portions, decode tokens of several requests in one step, few pages
     sched, ends = helpers.mixed(lengths, prompt_lens, seed=5)
     got = {}
     res = helpers.run_schedule(runner(helpers.peak_pages(sched, ends, ps)), toks, sched, ends, prompt_lens=prompt_lens,
-                               selective=True, planned=got)
+                               planned=got)
     check(res, got, "mixed")
 
 
@@ -94,12 +94,12 @@ def test_chosen_pages_equal_the_plain_ones(model_folders):
     toks = helpers.random_tokens(n, plain.cfg.vocab, 77)
     plain.forward(toks, Selective([1], k, 2, 1.0, ps, pl))
     want = plain.last_selection
-    r = ModelRunner(folder, engine_config=EngineConfig(max_batch=2, max_seq_len=128, page_size=ps, dtype="float32", selective=sel))
+    r = ModelRunner(folder, engine_config=EngineConfig(max_batch=2, max_seq_len=128, page_size=ps, dtype="float32", options=dict(selective_cache=sel)))
     slot = r.cache.acquire_slot()
     r.run_rows([RowInput(slot, toks[:pl], 0, [])])
     checked = 0
     for p in range(pl, n):
-        r.run_rows([RowInput(slot, toks[p:p + 1], p, [0], selective=True)])
+        r.run_rows([RowInput(slot, toks[p:p + 1], p, [0], flags=1)])
         count = int(r.cache.states[SELECTED_COUNT][slot])
         if (2, p) in want:
             assert count == k
