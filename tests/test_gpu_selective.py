@@ -5,7 +5,7 @@ import torch
 
 import helpers
 from plain_yi import PlainYi, Selective
-from test_gpu_model import TOL, compare
+from test_gpu_model import compare
 
 pytestmark = pytest.mark.gpu
 
