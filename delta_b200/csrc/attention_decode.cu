@@ -556,6 +556,25 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
 }
 
+// Raises the kernel's limit of dynamic shared memory to ``smem`` bytes on the current device when it is
+// lower (the attribute belongs to the device's copy of the kernel; setting it anew would also lower it).
+template <int HD, bool LOW, bool TMA>
+int configure(size_t smem) {
+  static size_t configured_on[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  size_t& configured = configured_on[dev & 63];
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    configured = smem;
+  }
+  return 0;
+}
+
 template <int HD, bool LOW, bool TMA>
 int launch(const DkAttnParams& pin, cudaStream_t stream) {
   DkAttnParams p = pin;
@@ -579,18 +598,7 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     DK_REQUIRE(make_tensor_map_bf16_4d(&map_run, p.kv, dims, strides, p.ps, TILE / p.ps),
                "attention_decode: cannot encode the tensor map of runs of pages");
   }
-  static size_t configured_on[64] = {0};     // per device: the attribute belongs to the device's copy of the kernel
-  int dev = 0;
-  cudaGetDevice(&dev);
-  size_t& configured = configured_on[dev & 63];
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      dk_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-      return DK_ERR_LAUNCH;
-    }
-    configured = smem;
-  }
+  if (int rc = configure<HD, LOW, TMA>(smem)) return rc;
   dim3 grid(p.splits, p.KV, p.rows);
   attention_decode_kernel<HD, LOW, TMA><<<grid, NTHREADS, smem, stream>>>(map_run, p);
   int rc = dk_check_launch("attention_decode");
@@ -615,17 +623,22 @@ extern "C" int dk_attention_decode_blocks_per_sm(int H, int KV, int hd, int bloc
   const size_t merge_bytes = (size_t)NWARPS * 16 * hd * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
   const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
   const bool low = H / KV <= 8;
-  int n = 0;
+  int n = 0, rc;
   cudaError_t e;
-  if (hd == 64) {
-    auto k = low ? attention_decode_kernel<64, true, false> : attention_decode_kernel<64, false, false>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, NTHREADS, smem);
+  if (hd == 64 && low) {
+    rc = configure<64, true, false>(smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_kernel<64, true, false>, NTHREADS, smem);
+  } else if (hd == 64) {
+    rc = configure<64, false, false>(smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_kernel<64, false, false>, NTHREADS, smem);
+  } else if (low) {
+    rc = configure<128, true, false>(smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_kernel<128, true, false>, NTHREADS, smem);
   } else {
-    auto k = low ? attention_decode_kernel<128, true, false> : attention_decode_kernel<128, false, false>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, NTHREADS, smem);
+    rc = configure<128, false, false>(smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_decode_kernel<128, false, false>, NTHREADS, smem);
   }
+  if (rc != 0) return 0;
   if (e != cudaSuccess) {
     dk_set_error("attention_decode: occupancy query failed: %s", cudaGetErrorString(e));
     return 0;

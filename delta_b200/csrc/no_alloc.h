@@ -27,7 +27,8 @@ extern "C" {
 //  * A launch that needs more than DK_STATIC_SCRATCH_FLOATS floats is refused with
 //    DK_ERR_ARG (-1) and a message in dk_last_error(); use fewer splits or rows.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress)
-//    and keeps it; make that first call before any stream capture begins.
+//    and keeps it; make that first call before any stream capture begins.  "The device" is
+//    the one that is current when the call is made: make the stream's device current first.
 //  * All calls share the one array per device.  It still holds what the last call left, but
 //    nothing has to be cleared: every block writes its own slot before the merge reads it.
 //    Two calls that overlap on the GPU (different streams) would write the same slots and

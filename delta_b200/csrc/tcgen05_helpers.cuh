@@ -34,14 +34,14 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
   return t;
 }
-// false when the wait gave up: after WAIT_LIMIT_NS, or after SPIN_ROUNDS rounds of 256 tries
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// false when the wait gave up: after limit_ns, or after SPIN_ROUNDS rounds of 256 tries
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t round = 0; round < SPIN_ROUNDS; ++round) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
   return false;
 }

@@ -74,6 +74,12 @@ def raise_if_error(err: torch.Tensor) -> None:
         raise KernelError(error_text(code, a, b, c))
 
 
+def wait_check(err: torch.Tensor, limit_ms: float = 1.0) -> None:
+    """Launches a kernel whose only wait, bounded by ``limit_ms`` (at most 10), can never be satisfied:
+    it gives up, records it in ``err`` and returns.  For checking that path; nothing else uses it."""
+    _l.check(_l.load().dk_wait_check(_ptr(err, "err", torch.int32), int(limit_ms * 1e6), _stream()), "wait_check")
+
+
 # ---------------------------------------------------------------------------
 
 def embedding(tokens, table, out, err=None):

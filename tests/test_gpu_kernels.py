@@ -30,6 +30,19 @@ def i32(x):
     return torch.tensor(x, dtype=torch.int32, device=DEV)
 
 
+def assert_heads_close(got, ref, H, hd, what="", rel=1e-2):
+    """Per (token, head): the difference's norm is at most ``rel`` times the reference's norm.  An
+    absolute bound would let a kernel drop a page among hundreds of keys: the output there is a mean
+    of many values and small all over."""
+    g = got.float().cpu().reshape(-1, H, hd)
+    r = ref.float().cpu().reshape(-1, H, hd)
+    err = (g - r).norm(dim=-1)
+    bad = (err > rel * r.norm(dim=-1) + 1e-6).nonzero()
+    if bad.numel():
+        t, h = int(bad[0, 0]), int(bad[0, 1])
+        raise AssertionError(f"{what}: token {t}, head {h}: |difference| {err[t, h].item():.3e} against |reference| {r[t, h].norm().item():.3e}")
+
+
 # ------------------------------------------------------------------ elementwise
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -274,7 +287,10 @@ def test_gemm_small_m_refuses_what_it_does_not_take():
 class PagedCase:
     """Random requests in a random paged cache, with the plain float32 answer."""
 
-    def __init__(self, dtype, H, KV, hd, ps, seq_lens, q_lens, seed=0, scatter=True):
+    def __init__(self, dtype, H, KV, hd, ps, seq_lens, q_lens, seed=0, scatter=True, counting=False):
+        """``counting``: queries are zero, so every key a row may read weighs the same, and the value of
+        a key is the unit vector of its page's number (modulo the head size): the output then counts,
+        exactly, how many keys of which pages were read."""
         g = torch.Generator(device="cpu").manual_seed(seed)
         self.dtype, self.H, self.KV, self.hd, self.ps = dtype, H, KV, hd, ps
         self.seq_lens, self.q_lens = seq_lens, q_lens
@@ -287,6 +303,10 @@ class PagedCase:
         self.k = [torch.randn(n, KV, hd, generator=g).to(dtype) for n in seq_lens]
         self.v = [torch.randn(n, KV, hd, generator=g).to(dtype) for n in seq_lens]
         self.q = [torch.randn(ql, H, hd, generator=g).to(dtype) for ql in q_lens]
+        if counting:
+            self.q = [torch.zeros_like(q) for q in self.q]
+            self.v = [torch.nn.functional.one_hot((torch.arange(n) // ps) % hd, hd).to(dtype)[:, None, :].repeat(1, KV, 1)
+                      for n in seq_lens]
         kv = torch.zeros(total + 3, 2, KV, ps, hd, dtype=dtype)
         bt = torch.full((B, max_pages), -1, dtype=torch.int32)
         nxt = 0
@@ -404,15 +424,15 @@ def test_attention_decode_against_plain(G, KV, hd, ps, pages):
         scratch = torch.empty(max(n, 1), device=DEV)
         p = case.params(out, lse=lse, scratch=scratch, splits=splits)
         o.attention_decode(p)
-        assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2), f"splits={splits}"
-        assert torch.allclose(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
-        assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+        assert_heads_close(out, ref, H, hd, f"splits={splits}")
+        assert_heads_close(out, plain, H, hd, f"splits={splits}, against the plain kernel")
+        assert torch.allclose(lse.cpu(), ref_lse, atol=1e-3, rtol=1e-5)
     # a window whose edge lies inside a page, and beyond the first pages
     out = torch.empty_like(plain)
     scratch = torch.empty(o.attention_decode_scratch_floats(case.T, H, hd, 3), device=DEV)
     o.attention_decode(case.params(out, window=ps + 5, scratch=scratch, splits=3))
     refw, _, _ = case.reference(window=ps + 5)
-    assert torch.allclose(out.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out, refw, H, hd, "window")
 
 
 @pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_runs"])
@@ -438,8 +458,8 @@ def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
     err = o.new_error_record(DEV)
     prefill(case.params(out, lse=lse, err=err), max(q_lens))
     assert err.cpu().tolist() == [0, 0, 0, 0]
-    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
-    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+    assert_heads_close(out, ref, H, hd, kernel)
+    assert torch.allclose(lse.cpu(), ref_lse, atol=1e-3, rtol=1e-5)
     # single tokens are skipped with row_filter 2 and taken by the decode kernel with row_filter 1
     out2 = torch.zeros_like(out)
     prefill(case.params(out2, row_filter=2), max(q_lens))
@@ -450,17 +470,17 @@ def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
         o.attention_decode(case.params(out2, row_filter=1, scratch=scratch, splits=2))
     else:
         out2[singles] = out[singles]
-    assert torch.allclose(out2.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out2, ref, H, hd, "singles by the decode kernel")
     # a window whose edge lies inside a tile and inside a page
     out3 = torch.zeros_like(out)
     prefill(case.params(out3, window=ps + 7), max(q_lens))
     refw, _, _ = case.reference(window=ps + 7)
-    assert torch.allclose(out3.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out3, refw, H, hd, "window inside a tile")
     # a window of several tiles, whose far edge lies inside a tile
     out4 = torch.zeros_like(out)
     prefill(case.params(out4, window=300), max(q_lens))
     refw, _, _ = case.reference(window=300)
-    assert torch.allclose(out4.float().cpu(), refw, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out4, refw, H, hd, "window of several tiles")
 
 
 def test_attention_prefill_tc_long_rows_and_maximum_that_grows():
@@ -484,8 +504,8 @@ def test_attention_prefill_tc_long_rows_and_maximum_that_grows():
     err = o.new_error_record(DEV)
     o.attention_prefill_tc(case.params(out, lse=lse, err=err), max(q_lens))
     assert err.cpu().tolist() == [0, 0, 0, 0]
-    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
-    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-3)
+    assert_heads_close(out, ref, H, hd, "long rows")
+    assert torch.allclose(lse.cpu(), ref_lse, atol=1e-3, rtol=1e-5)
 
 
 @pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (3, 2, 64, 8), (16, 1, 128, 32)])
@@ -554,14 +574,14 @@ def test_attention_on_chosen_pages_and_score_dump(kernel):
     scratch = torch.empty(max(1, o.attention_decode_scratch_floats(B, H, hd, 2)), device=DEV)
     run(case.params(out, row_flags=flags, sel_pages=sel_pages, sel_count=sel_count, scratch=scratch, splits=2 if kernel == "decode" else 0))
     ref, _, _ = case.reference(pages=[chosen[b] for b in range(B)])
-    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out, ref, H, hd, "chosen pages")
     # the dump of a planner layer
     stride = 304
     dump = torch.full((B, H, stride), float("nan"), device=DEV)
     lse = torch.empty(B, H, device=DEV)
     run(case.params(out, row_flags=flags, dump=dump, lse=lse, scratch=scratch, splits=2 if kernel == "decode" else 0))
     ref, ref_lse, scores = case.reference()
-    assert torch.allclose(out.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+    assert_heads_close(out, ref, H, hd, "with a dump")
     for b, n in enumerate(seq_lens):
         if b == 2:
             assert torch.isnan(dump[b]).all()                       # not flagged: nothing is dumped
