@@ -1,12 +1,17 @@
-"""The plain implementation against outputs of hoenza/DELTA's own code (stored by
-tests/golden/make_golden.py), for the parts of it that run on a CPU."""
+"""The plain implementation against outputs of hoenza/DELTA's own code: the parts of it that run
+on a CPU (stored by tests/golden/make_golden.py), and the logits of its whole model on a GPU, run
+through its own entry point on a tiny random model (stored by
+tests/golden/make_reference_model_golden.py)."""
+import sys
 from pathlib import Path
 
+import pytest
 import torch
 
 import plain_yi as P
 
-G = torch.load(Path(__file__).resolve().parent / "golden" / "reference_parts.pt")
+GOLDEN = Path(__file__).resolve().parent / "golden"
+G = torch.load(GOLDEN / "reference_parts.pt")
 
 
 def test_rms_norm_float32():
@@ -56,3 +61,59 @@ def test_page_selection():
             ref = (case["indices"][ptr[b]:ptr[b + 1]] - 100 - base).tolist()
             assert mine == ref, (k, L, b, mine, ref)
             base += n
+
+
+# ---- the whole model: rotary positions, cache append, attention, layer order, output matrix --------
+
+@pytest.fixture(scope="module")
+def reference_model(tmp_path_factory):
+    """(stored logits of the reference, the tiny model folder they were made from, written again here
+    from its configuration and seed and checked against the stored checksum of the weights)."""
+    sys.path.insert(0, str(GOLDEN))
+    from make_reference_model_golden import checksum
+    from delta_b200.weights import write_random_model
+    import delta_b200.models  # noqa: F401
+    M = torch.load(GOLDEN / "reference_model_logits.pt")
+    folder = write_random_model(tmp_path_factory.mktemp("golden") / "hf", M["config"], M["seed"], torch.float32)
+    if checksum(P.read_safetensors_plain(folder / "model.safetensors")) != M["weights_sha256"]:
+        pytest.skip("this torch draws other random weights from the seed than the one the stored logits were made with")
+    return M, folder
+
+
+def test_whole_model_logits_equal_the_reference(reference_model):
+    """The reference ran a converted checkpoint (q and k rows in neighbour pairs) with its
+    neighbour-pair rotation in bfloat16; the plain implementation reads the unconverted folder and
+    rotates pairs (j, j + head/2).  Every position's logits agree to the rounding of bfloat16
+    (0.9 % of the largest logit is the worst seen; the bound is 1.5 %), prompts of 40, 23 and 1
+    tokens and 24 decoded tokens each, and the greedy tokens follow."""
+    M, folder = reference_model
+    plain = P.PlainYi(folder, rounding="bfloat16")
+    for i, (prompt, out) in enumerate(zip(M["prompts"], M["outputs"])):
+        ref = M["logits"][i].float()
+        got = plain.forward(prompt + out[:-1])
+        assert got.shape == ref.shape
+        scale = ref.abs().max().item()
+        err = (got - ref).abs().amax(dim=-1)
+        assert err.max().item() <= 0.015 * scale, f"request {i}: position {int(err.argmax())} differs by {err.max().item():.4f} (largest logit {scale:.3f})"
+        # greedy tokens, wherever the reference's best two logits are further apart than the rounding
+        top = ref.topk(2, dim=-1).values
+        clear = (top[:, 0] - top[:, 1]) > 0.03 * scale
+        assert bool((got.argmax(-1) == ref.argmax(-1))[clear].all()) and int(clear.sum()) > len(prompt) // 2
+
+
+def test_the_other_pairing_or_head_mapping_would_not_pass(reference_model):
+    """What the comparison above is able to see: neighbour-pair rotation on the unconverted rows, or
+    query heads mapped to key-value heads the other way round, miss the reference by several bounds."""
+    M, folder = reference_model
+    prompt, out = M["prompts"][0], M["outputs"][0]
+    ref = M["logits"][0].float()
+    scale = ref.abs().max().item()
+    wrong = P.PlainYi(folder, rounding="bfloat16", interleaved=True).forward(prompt + out[:-1])
+    assert (wrong - ref).abs().max().item() > 0.04 * scale
+    swapped = P.PlainYi(folder, rounding="bfloat16")
+    c = swapped.cfg
+    for l in range(c.layers):       # exchange the two key-value heads: query heads 0,1 then read what belongs to 2,3
+        for name in ("k_proj", "v_proj"):
+            w = swapped.w[f"model.layers.{l}.self_attn.{name}.weight"]
+            swapped.w[f"model.layers.{l}.self_attn.{name}.weight"] = w.view(c.kv_heads, c.head_dim, -1).flip(0).reshape(w.shape)
+    assert (swapped.forward(prompt + out[:-1]) - ref).abs().max().item() > 0.04 * scale
