@@ -249,3 +249,30 @@ def test_waves_of_requests_repeat_their_outputs(model_folders):
         e.runner.cache.check()
         assert all(v == 0 for v in e.runner.cache.pages_in_use().values())
     assert set(e.runner._graphs) >= {8, 12, 16, 20}
+
+
+def test_a_failed_graph_recording_falls_back_to_eager_steps(model_folders, monkeypatch):
+    """When recording a decode step fails, that batch size runs eagerly from then on, the reason is
+    counted, and the tokens are the ones of the engine without CUDA graphs."""
+    from delta_b200.engine import LMBackend
+    folder = model_folders["A"]
+    vocab = PlainYi(folder).cfg.vocab
+    prompts = [helpers.random_tokens(n, vocab, 600 + i) for i, n in enumerate([12, 30, 7])]
+
+    def run(graphs):
+        e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=graphs)
+        e.load_model(folder)
+        e.setup_caches(max_batch_size=3, max_seq_length=64, page_size=16)
+        return e.generate(prompts, 12), e
+
+    want, _ = run(False)
+
+    class Refuses:
+        def __init__(self, *a, **k):
+            raise RuntimeError("recording is refused in this test")
+    monkeypatch.setattr(torch.cuda, "CUDAGraph", Refuses)
+    got, e = run(True)
+    assert got == want
+    assert e.runner.graph_captures == 0 and e.runner.graph_replays == 0
+    assert sum(e.runner.graph_fallbacks.values()) >= 8 and all("capture failed" in k for k in e.runner.graph_fallbacks)
+    assert "refused" in e.runner._graphs[3]["error"]
