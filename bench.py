@@ -25,9 +25,24 @@ step.  It prints ONE JSON line:
              live requests) / its time, against the copy bandwidth
   points     decode tokens per second at batch 1 and 64
 
-Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else
-from the fallback figures of an earlier measurement on this pool.  The engine runs on
-one GPU only: for --gpus above 1 it says so and exits with 2.
+Peaks come from MEASURED_PEAKS.json beside this file when it is there, else from the
+fallback figures of an earlier measurement of a B200.  The engine runs on one GPU
+only: for --gpus above 1 it says so and exits with 2.
+
+Other workloads (``--workload``), each printing one JSON line of the same shape:
+
+  baseline     2,048-token prompts and 512 generated tokens each through ``run_scheduler_loop`` at
+               batch 1, 8 and 64 (Yi-6B shape): tokens per second = generated tokens / time of the
+               decode steps, and the same over the wall clock of the whole loop
+  yi9b-long    Yi-1.5-9B shape, 16 requests of 256 + 3,584 tokens, once with the full cache and
+               once with DELTA (``--full_cache_layers 2 --subset_cache_size 64``); both rates and
+               their ratio
+  yi34b-mixed  Yi-34B shape: steps of one 2,048-token prompt portion beside up to 63 decoding
+               requests; milliseconds per mixed step, tokens per second of both kinds, and the
+               portion's share of the tensor-core peak
+
+``--impl reference`` runs the unmodified hoenza/DELTA engine (baseline/reference_arm.py) on the
+default workload and prints its line.
 """
 from __future__ import annotations
 
@@ -163,6 +178,144 @@ def reference_arm(args) -> int:
     return unavailable(f"the reference ended with code {r.returncode}: {tail}")
 
 
+def _flat_config(shape_name, cfg, layers, **more) -> dict:
+    d = cfg["hidden_size"]
+    out = {"model": shape_name, "layers": layers, "layers_of_named_config": cfg["num_hidden_layers"], "hidden": d,
+           "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+           "head_dim": cfg.get("head_dim") or d // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+           "vocab": cfg["vocab_size"], "page_size": 16, "parallelism": "single GPU"}
+    out.update(more)
+    return out
+
+
+def _loop(eng, prompts, max_new, timed: bool):
+    """Runs the requests through ``run_scheduler_loop``.  Timed: every step between CUDA events
+    (returns the decode steps' records); untimed: as a user runs it, wall clock only."""
+    import torch
+    eng.step_timings.clear()
+    eng.record_timings = timed
+    eng.add_requests(prompts, [len(p) + max_new for p in prompts], [], max_new_tokens=max_new)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eng.run_scheduler_loop()
+    wall = time.perf_counter() - t0
+    eng.record_timings = False
+    decode = [r for r in eng.step_timings if r["tokens"] == r["active_bsz"]]
+    return decode, wall
+
+
+def other_workload(args) -> int:
+    import torch
+    from delta_b200.engine import LMBackend
+    from delta_b200.kernels import ops
+    pk = peaks()
+    gen = torch.Generator().manual_seed(1)
+    name = args.workload
+    shape = {"baseline": "yi-6b", "yi9b-long": "yi-9b", "yi34b-mixed": "yi-34b"}[name]
+    shape_name, shape_cfg = SHAPES[shape]
+    layers = args.layers or shape_cfg["num_hidden_layers"]
+    cfg = dict(shape_cfg, num_hidden_layers=layers)
+    weight_bytes, kv_per_tok, prefill_flops = model_numbers(cfg, layers)
+
+    def prompts(n, length):
+        return [torch.randint(0, cfg["vocab_size"], (length,), generator=gen).tolist() for _ in range(n)]
+
+    def engine(max_batch, max_len, **kw):
+        e = LMBackend(dtype=torch.bfloat16, device="cuda:0", cuda_graph_decode=not args.no_graph)
+        e.load_model(config_json=cfg, seed=0)
+        e.setup_caches(max_batch_size=max_batch, max_seq_length=max_len, page_size=16, **kw)
+        e.scheduler.decode_while_prefill = False
+        return e
+
+    clocks = ClockSampler()
+    if name == "baseline":
+        plen, new = 2048, args.generate or 512
+        eng = engine(64, plen + new, max_tokens_per_step=2048)
+        points, e2e, ms = {}, {}, {}
+        clocks.start()
+        for b in (1, 8, 64):
+            _loop(eng, prompts(b, plen), 24, True)                     # records the graphs of this batch size
+            decode, _ = _loop(eng, prompts(b, plen), new, True)
+            full = [r for r in decode if r["active_bsz"] == b]
+            t = sum(r["model_forward_ms"] + r["postprocess_ms"] for r in full)
+            points[f"decode_b{b}"] = b * len(full) / (t / 1e3)
+            ms[f"b{b}"] = t / len(full)
+            l0 = ops.launch_count()
+            _, wall = _loop(eng, prompts(b, plen), new, False)
+            e2e[f"b{b}"] = b * new / wall        # prompts included in the time: what a user of the loop sees
+        clk = clocks.stop()
+        ctx = plen + new / 2
+        achieved = (weight_bytes + 8 * ctx * kv_per_tok) / (ms["b8"] / 1e3) / 1e9
+        out = {"workload": name, "metric": f"decode tok/s ({shape_name}, bf16, 2,048-token prompts + {new} generated, batch 1/8/64)",
+               "value": points["decode_b8"], "unit": "tokens/s", "n_gpus": 1, "ms_per_step": ms["b8"], "higher_is_better": True,
+               "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+               "config": _flat_config(shape_name, shape_cfg, layers, global_batch=8, seq_len=plen + new, prompt_len=plen,
+                                      generated=new, cuda_graph_decode=not args.no_graph, peaks=pk["source"]),
+               "points": points, "ms_per_decode_step": ms,
+               "e2e": {"unit": "generated tokens/s over the wall clock of the whole loop, prompts included", **e2e},
+               "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+               "clocks": clk}
+    elif name == "yi9b-long":
+        B, plen, new = 16, 256, args.generate or 3584
+        res = {}
+        clocks.start()
+        for mode in ("full", "delta"):
+            eng = engine(B, plen + new, max_tokens_per_step=4096, enable_selective_cache=mode == "delta",
+                         full_cache_layers=[2] if mode == "delta" else None, subset_cache_size=64)
+            _loop(eng, prompts(B, plen), 24, True)
+            decode, _ = _loop(eng, prompts(B, plen), new, True)
+            t = sum(r["model_forward_ms"] + r["postprocess_ms"] for r in decode)
+            _, wall = _loop(eng, prompts(B, plen), new, False)
+            tail = decode[-max(1, len(decode) // 8):]       # the last eighth: the longest contexts
+            res[mode] = dict(tokens_per_s=B * len(decode) / (t / 1e3), ms_per_step=t / len(decode),
+                             ms_per_step_last_eighth=sum(r["model_forward_ms"] + r["postprocess_ms"] for r in tail) / len(tail),
+                             e2e_tokens_per_s=B * new / wall, steps=len(decode))
+            del eng
+            torch.cuda.empty_cache()
+        clk = clocks.stop()
+        out = {"workload": name, "metric": f"decode tok/s ({shape_name}, bf16, batch {B}, {plen}-token prompts + {new} generated)",
+               "value": res["delta"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "ms_per_step": res["delta"]["ms_per_step"],
+               "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+               "config": _flat_config(shape_name, shape_cfg, layers, global_batch=B, seq_len=plen + new, prompt_len=plen,
+                                      generated=new, full_cache_layers="2", subset_cache_size=64, cuda_graph_decode=not args.no_graph),
+               "full_cache": res["full"], "delta": res["delta"],
+               "delta_over_full": res["delta"]["tokens_per_s"] / res["full"]["tokens_per_s"], "clocks": clk}
+    else:
+        B, portion, ctx_len = 64, 2048, 4096
+        eng = engine(B, ctx_len, max_tokens_per_step=portion + B)
+        eng.scheduler.decode_while_prefill = True
+        n_mixed = max(4, min(args.steps, 12))
+        # 63 requests decode from a context of 1,024 tokens on; then one prompt of 2,048 tokens is added per step
+        eng.add_requests(prompts(B - 1, 1024), [ctx_len] * (B - 1), [])
+        while eng.scheduler.waiting or any(not r.output for r in eng.scheduler.running):
+            eng.step()
+        for _ in range(4):
+            eng.step()
+        records = []
+        clocks.start()
+        eng.record_timings = True
+        for k in range(n_mixed + 2):
+            eng.add_requests(prompts(1, portion), [portion + 1], [])     # ends after its first token: its slot is free again
+            eng.step_timings.clear()
+            eng.step()
+            records.extend(eng.step_timings)
+        eng.record_timings = False
+        clk = clocks.stop()
+        mixed = [r for r in records if r["tokens"] > portion][2:]
+        t = sum(r["model_forward_ms"] + r["postprocess_ms"] for r in mixed) / len(mixed)
+        dec = sum(r["active_bsz"] - 1 for r in mixed) / len(mixed)
+        out = {"workload": name, "metric": f"mixed step ({shape_name}, bf16): one {portion}-token prompt portion beside {B - 1} decoding requests",
+               "value": (portion + dec) / (t / 1e3), "unit": "tokens/s", "n_gpus": 1, "ms_per_step": t, "higher_is_better": True,
+               "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+               "config": _flat_config(shape_name, shape_cfg, layers, global_batch=B, seq_len=ctx_len, portion=portion, steps=len(mixed)),
+               "prefill_tokens_per_s": portion / (t / 1e3), "decode_tokens_per_s": dec / (t / 1e3),
+               "chunk": {"flops": prefill_flops(portion), "frac": prefill_flops(portion) / (t / 1e3) / (pk["bf16_tflops"] * 1e12),
+                         "peak_tflops": pk["bf16_tflops"]},
+               "weights_gb": weight_bytes / 1e9, "clocks": clk}
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -178,6 +331,8 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed"], default="decode")
+    ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -186,6 +341,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload != "decode":
+        return other_workload(args)
 
     import torch
     from delta_b200.engine import LMBackend
@@ -289,12 +446,9 @@ def main() -> int:
         "metric": f"decode tok/s ({shape_name}, bf16, batch {args.batch}, context {ctx_len})", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
-        "config": {"model": shape_name, "layers": args.layers, "layers_of_named_config": full_layers,
-                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-                   "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "global_batch": args.batch, "seq_len": ctx_len, "page_size": 16, "parallelism": "single GPU",
-                   "cuda_graph_decode": not args.no_graph, "selective_cache": bool(args.enable_selective_cache), "l2": "inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9),
-                   "peaks": pk["source"]},
+        "config": _flat_config(shape_name, shape_cfg, args.layers, global_batch=args.batch, seq_len=ctx_len,
+                               cuda_graph_decode=not args.no_graph, selective_cache=bool(args.enable_selective_cache),
+                               l2="inputs larger than L2 (weights %.1f GB)" % (weight_bytes / 1e9), peaks=pk["source"]),
         "e2e": {"value": args.batch / (e2e_ms[1] / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "value_tokens_fed_back_through_host": args.batch / (e2e_ms[0] / 1e3)},
         "gpu_launches": int(round(launches * args.steps)),
