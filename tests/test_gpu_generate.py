@@ -123,6 +123,32 @@ def test_command_line(model_folders, tmp_path):
     assert res["summary"]["generated_tokens"] == 30 and len(res["results"]) == 5
 
 
+def test_command_line_step_timings_and_tuning_file(model_folders, tmp_path):
+    """--step_timings writes logs/step_timings_<time>.json with the reference's five timing names and a meta
+    block; --tuning_file saves the measured kernel choices and a second run reads them back."""
+    import os
+    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    tune = tmp_path / "tune.json"
+    cmd = [sys.executable, "-m", "delta_b200.cli", "--model", str(model_folders["D"]), "--B", "3", "--max_len", "128",
+           "--dataset", "random", "--prompt_len", "24", "--num_samples", "3", "--max_new_tokens", "10", "--cuda_graph_decode",
+           "--step_timings", "--tuning_file", str(tune)]
+    for run in range(2):
+        r = subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        summary = json.loads(r.stdout.strip().splitlines()[-1])
+        assert summary["generated_tokens"] == 30 and summary["graph_replays"] > 0 and summary["graph_fallbacks"] == {}
+        rec = json.loads((tmp_path / summary["step_timings_file"]).read_text())
+        assert {"collect_pages_ms", "plan_ms", "model_forward_ms", "postprocess_ms", "step_total_ms", "active_bsz", "total_pages"} <= set(rec["steps"][0])
+        assert rec["meta"]["steps"] == len(rec["steps"]) and "summary" in rec["meta"]
+        assert all(s["collect_pages_ms"] >= 0 and s["model_forward_ms"] > 0 for s in rec["steps"])
+        choices = json.loads(tune.read_text())["product_kernels"]
+        assert choices and all(c["kernel"] for c in choices)
+        if run == 0:
+            first = {(c["rows"], c["n"], c["k"], c["swiglu"]): c["kernel"] for c in choices}
+        else:       # the second run took the saved choices: none differs
+            assert first == {(c["rows"], c["n"], c["k"], c["swiglu"]): c["kernel"] for c in choices if (c["rows"], c["n"], c["k"], c["swiglu"]) in first}
+
+
 @pytest.mark.parametrize("selective", [False, True])
 def test_cuda_graph_decode_gives_the_same_tokens(model_folders, selective):
     """Decode steps replayed from a CUDA graph generate what eager steps generate, with
