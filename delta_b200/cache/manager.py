@@ -193,11 +193,6 @@ class CacheManager:
                 g.first_page[slot] = first_needed
 
     # ---- views for a step ------------------------------------------------------
-    def block_tables_for(self, slots: List[int]) -> Dict[str, np.ndarray]:
-        """group name -> [len(slots), max_pages] int32 block tables of these slots (a copy)."""
-        return {n: g.table[slots] if len(slots) else np.zeros((0, self.max_pages_per_request), np.int32)
-                for n, g in self.groups.items()}
-
     def layer_pages(self, cache_id: int) -> torch.Tensor:
         g = self.group_of_cache[cache_id]
         return g.pages[g.index_of[cache_id]]

@@ -38,9 +38,6 @@ class PagePool:
     def held_pages(self) -> int:
         return self.num_pages - len(self._free)
 
-    def can_alloc(self, n: int) -> bool:
-        return n <= len(self._free)
-
     def alloc(self, n: int) -> List[int]:
         """n pages, or ``OutOfPages`` with nothing taken."""
         if n < 0:

@@ -398,23 +398,3 @@ extern "C" int dk_rope_append(void* qkv, const int* tok_pos, const int* tok_row,
 #undef LAUNCH
   return dk_check_launch("rope_append");
 }
-
-// ------------------------------------------------------------- row gather
-// out[r, :] = x[rows[r], :]; float output whatever the input type (used to hand
-// out logits and hidden rows).
-template <typename T>
-__global__ void gather_rows_f32_kernel(const T* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out, int d) {
-  const int r = blockIdx.x;
-  const T* src = x + (size_t)rows[r] * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)r * d + i] = to_f32<T>(src[i]);
-}
-
-extern "C" int dk_gather_rows_f32(const void* x, const int* rows, float* out, int n_rows, int d, int dtype,
-                                  cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  DK_REQUIRE(n_rows > 0 && d > 0, "gather_rows: bad sizes");
-  if (dtype == DK_F32) gather_rows_f32_kernel<float><<<n_rows, 256, 0, stream>>>((const float*)x, rows, out, d);
-  else if (dtype == DK_BF16) gather_rows_f32_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>((const __nv_bfloat16*)x, rows, out, d);
-  else DK_REQUIRE(false, "gather_rows: unknown dtype %d", dtype);
-  return dk_check_launch("gather_rows");
-}

@@ -41,7 +41,6 @@ _SIGNATURES = {
     "dk_rms_norm": [P, P, P, P, P, I, I, F, I, I, I, P],
     "dk_silu_mul": [P, P, I, I, I, P],
     "dk_rope_append": [P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, P, P],
-    "dk_gather_rows_f32": [P, P, P, I, I, I, P],
     "dk_gemm_nt_plain": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_attention_plain": [C.POINTER(AttnParams), P],
     "dk_recent_pages": [P, P, P, P, P, P, I, I, I, D, P],

@@ -130,12 +130,6 @@ def rope_append(qkv, tok_pos, tok_row, block_table, kv, table, H, KV, hd, ps, in
         _ptr(err, "err", torch.int32), _stream()), "rope_append")
 
 
-def gather_rows_f32(x, rows, out):
-    _l.check(_l.load().dk_gather_rows_f32(_ptr(x, "x"), _ptr(rows, "rows", torch.int32), _ptr(out, "out", torch.float32),
-                                          out.shape[0], x.shape[1], dtype_code(x.dtype), _stream()), "gather_rows")
-    return out
-
-
 def gemm_nt_plain(a, w, out):
     """out[M,N] = a[M,K] @ w[N,K]^T on the FMA units with float accumulation."""
     M, K = a.shape

@@ -96,12 +96,8 @@ class Model:
             block = self.blocks[e.layer]
             cache = ctx.cache_view(e.cache, e.writes_cache) if block.cache_spec() is not None else None
             x, pending = block.forward(ctx, x, pending, cache)
-            if ctx.capture is not None and ctx.capture.get("want_hidden"):
-                ctx.capture.setdefault("hidden", []).append((x.clone(), None if pending is None else pending.clone()))
         R = ctx.logit_rows.shape[0]
-        if R == 0:
-            if pending is not None:
-                pass  # nothing reads the stream after the last layer
+        if R == 0:      # nothing reads the stream after the last layer
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
         h = self.final_norm.forward(ctx, x, add=pending, rows=ctx.logit_rows)
         return linear.linear(ctx, h, self.lm_head, out_dtype=torch.float32)

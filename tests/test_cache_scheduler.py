@@ -86,8 +86,7 @@ def test_the_padding_slot_holds_the_spare_page_and_no_pool_page():
     for g in m.groups.values():
         assert g.table[m.padding_slot, 0] == g.spare_page == 16 and (g.table[m.padding_slot, 1:] == -1).all()
         assert g.pool.free_pages == 16          # the spare page is not one of the pool's
-    tables = m.block_tables_for([slots[0], m.padding_slot])
-    assert all(int(t[1, 0]) == 16 for t in tables.values())
+    assert all(int(g.table[[slots[0], m.padding_slot]][1, 0]) == 16 for g in m.groups.values())
     m.check()
 
 
