@@ -70,8 +70,14 @@ def _decode(ctx, params, row_filter: int, group: str) -> None:
     longest = ctx.cache.max_seq_len if ctx.replayable else ctx.max_seq_len
     max_keys = longest if not params.window else min(longest, params.window + params.ps)
     rows = ctx.num_rows
-    per_sm = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, params.max_pages)
+    # blocks per SM depend on the page ids a block keeps in shared memory, which depend on the splits:
+    # ask for the occupancy without them, split, and ask again with what a block then holds
+    per_sm = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, 0)
     splits = decode_splits(rows, params.KV, max_keys, ctx.sm_count, per_sm)
+    held = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, -(-params.max_pages // splits))
+    if held < per_sm:
+        per_sm = held
+        splits = decode_splits(rows, params.KV, max_keys, ctx.sm_count, per_sm)
     params.splits = splits
     params.row_filter = row_filter
     # The variant that fetches runs of pages by TMA pays for finding the runs at the start of a block:

@@ -716,3 +716,23 @@ def test_product_tuner_keeps_the_preferred_kernel_within_the_margin(monkeypatch)
     assert tuned([10.0, 9.0] + [10.0] * (n - 2)) == cands[1]                               # 10 % faster
     assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.5]) == cands[1]                       # 5.6 % on the second: stays
     assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.0]) == cands[-1]
+
+
+def test_decode_attention_splits_follow_the_occupancy_at_long_contexts():
+    """The split count of the decode kernel comes from the device: SM count times the blocks of the kernel an
+    SM holds.  The page ids a block keeps in shared memory must be counted with the split count that is
+    chosen, not with the whole block table: at 32,768 keys the whole table would halve the occupancy, and
+    with it the splits, for nothing."""
+    from delta_b200.parts import attention_kernels as ak
+    o = ops()
+    sms = torch.cuda.get_device_properties(DEV).multi_processor_count
+    H, KV, hd, ps = 32, 4, 128, 16
+    free = o.attention_decode_blocks_per_sm(H, KV, hd, 0)
+    assert free >= 2
+    for rows, keys in ((8, 4096), (8, 32768), (1, 32768), (64, 4096)):
+        max_pages = keys // ps
+        splits = ak.decode_splits(rows, KV, keys, sms, free)
+        held = o.attention_decode_blocks_per_sm(H, KV, hd, -(-max_pages // splits))
+        assert held == free, (rows, keys, splits, held)        # the split's share of the table costs no occupancy
+        assert 1 <= splits <= ak.MAX_SPLITS and splits * rows * KV <= max(free * sms, rows * KV)
+    assert o.attention_decode_blocks_per_sm(H, KV, hd, 8192) < free    # the whole table of a 131,072-key request would
