@@ -54,6 +54,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--L", type=int, default=8, help="the newest L pages are always among the chosen")
     p.add_argument("--enable_selective_cache", action="store_true", help="DELTA on: layers outside --full_cache_layers read chosen pages")
     # added
+    p.add_argument("--count_page_ahead", action="store_true",
+                   help="count a request's pages as the reference does: one more, empty, once the newest is exactly full")
     p.add_argument("--random_weights", type=int, default=None, metavar="SEED", help="random weights instead of a folder's")
     p.add_argument("--config", type=Path, default=None, help="config.json for --random_weights")
     p.add_argument("--prompt_len", type=int, default=128)
@@ -100,7 +102,7 @@ def main(argv=None) -> int:
     eng.setup_caches(max_batch_size=args.B, max_seq_length=args.max_len, page_size=args.page_size, num_pages=args.num_pages,
                      max_tokens_per_step=args.max_tokens_per_step, enable_selective_cache=args.enable_selective_cache,
                      full_cache_layers=args.full_cache_layers, subset_cache_size=args.subset_cache_size,
-                     compression_ratio=args.compression_ratio, L=args.L)
+                     compression_ratio=args.compression_ratio, L=args.L, count_page_ahead=args.count_page_ahead)
     eng.throughput_mode = args.throughput_mode
     eng.record_timings = bool(args.step_timings)
     tok = None

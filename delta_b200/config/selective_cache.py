@@ -28,6 +28,12 @@ class SelectiveCacheConfig:
     compression_ratio: float = 1.0
     L: int = 8
     position_bias: float = 1e-7
+    # The reference takes a request's next page as soon as the newest is exactly full
+    # (DELTA/Engine/DELTA/scheduler.py:60-74), so at one position in ``page size`` its selection counts
+    # an empty page, which is always among the newest ``L`` and so takes one place of the subset.
+    # False: a request has the pages that hold its tokens.  True: counted as the reference counts
+    # them, for outputs that follow the reference's position by position.
+    count_page_ahead: bool = False
 
     def __post_init__(self):
         object.__setattr__(self, "full_cache_layers", tuple(sorted(set(int(i) for i in self.full_cache_layers))))
@@ -37,6 +43,8 @@ class SelectiveCacheConfig:
             raise ValueError("L must be at least 1: the page that holds the newest token is always read")
         if self.compression_ratio < 1.0:
             raise ValueError("compression_ratio must be at least 1")
+        if self.count_page_ahead and min(self.L, self.subset_cache_size) < 2:
+            raise ValueError("count_page_ahead needs L >= 2 and subset_cache_size >= 2: the empty page takes one place")
 
     @property
     def keep_last(self) -> int:

@@ -45,7 +45,7 @@ class LMBackend:
         self.cuda_graph_decode = bool(cuda_graph_decode)
         # the reference's scripts set these on model.config; here they are plain options
         self.options = SimpleNamespace(enable_selective_cache=False, full_cache_layers=None, subset_cache_size=1024,
-                                       compression_ratio=1.0, L=8)
+                                       compression_ratio=1.0, L=8, count_page_ahead=False)
         self._model_dir = None
         self._config_json = None
         self._seed = None
@@ -80,7 +80,7 @@ class LMBackend:
                      num_pages: Optional[int] = None, max_tokens_per_step: int = 2048,
                      enable_selective_cache: Optional[bool] = None, full_cache_layers=None,
                      subset_cache_size: Optional[int] = None, compression_ratio: Optional[float] = None,
-                     L: Optional[int] = None, check_kernel_errors: bool = True, rope_interleaved: bool = False,
+                     L: Optional[int] = None, count_page_ahead: Optional[bool] = None, check_kernel_errors: bool = True, rope_interleaved: bool = False,
                      shuffle_pages: Optional[int] = None):
         """``check_kernel_errors``: the kernels' error record (a bad page id, token id or position
         that a kernel skipped, a wait inside a kernel that ran out) travels to the host with every
@@ -96,10 +96,13 @@ class LMBackend:
             o.compression_ratio = compression_ratio
         if L is not None:
             o.L = L
+        if count_page_ahead is not None:
+            o.count_page_ahead = count_page_ahead
         selective = None
         if o.enable_selective_cache and o.full_cache_layers:
             selective = SelectiveCacheConfig(full_cache_layers=tuple(o.full_cache_layers), subset_cache_size=o.subset_cache_size,
-                                             compression_ratio=float(o.compression_ratio), L=o.L)
+                                             compression_ratio=float(o.compression_ratio), L=o.L,
+                                             count_page_ahead=bool(o.count_page_ahead))
         cfg = EngineConfig(max_batch=max_batch_size, max_seq_len=max_seq_length, page_size=page_size, num_pages=num_pages,
                            dtype=self.dtype, max_tokens_per_step=max_tokens_per_step,
                            cuda_graph_decode=self.cuda_graph_decode, check_kernel_errors=check_kernel_errors,

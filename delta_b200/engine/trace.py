@@ -53,6 +53,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--subset_cache_size", type=int, default=1024)
     ap.add_argument("--compression_ratio", type=float, default=1.0)
     ap.add_argument("--L", type=int, default=8)
+    ap.add_argument("--count_page_ahead", action="store_true",
+                    help="count a request's pages as the reference does: one more, empty, once the newest is exactly full")
     ap.add_argument("--dump-selected", action="store_true", help="write the pages each planner chose, per step")
     return ap
 
@@ -76,7 +78,8 @@ def main(argv=None) -> int:
     selective = None
     if args.enable_selective_cache and args.full_cache_layers:
         selective = SelectiveCacheConfig(full_cache_layers=tuple(args.full_cache_layers), subset_cache_size=args.subset_cache_size,
-                                         compression_ratio=args.compression_ratio, L=args.L)
+                                         compression_ratio=args.compression_ratio, L=args.L,
+                                         count_page_ahead=args.count_page_ahead)
     cfg = EngineConfig(max_batch=args.max_live, max_seq_len=max_tokens, page_size=args.page_size,
                        num_pages=args.num_pages if args.num_pages is not None else max_tokens // args.page_size,
                        dtype=args.dtype, max_tokens_per_step=max_tokens, cuda_graph_decode=args.cuda_graph_decode,

@@ -43,9 +43,9 @@ _SIGNATURES = {
     "dk_rope_append": [P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, P, P],
     "dk_gemm_nt_plain": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_attention_plain": [C.POINTER(AttnParams), P],
-    "dk_recent_pages": [P, P, P, P, P, P, I, I, I, D, P],
-    "dk_page_scores": [P, P, P, P, P, P, P, I, I, I, I, I, I, D, P],
-    "dk_select_pages": [P, P, P, P, P, P, P, I, I, I, I, I, F, D, P],
+    "dk_recent_pages": [P, P, P, P, P, P, I, I, I, D, I, P],
+    "dk_page_scores": [P, P, P, P, P, P, P, I, I, I, I, I, I, D, I, P],
+    "dk_select_pages": [P, P, P, P, P, P, P, I, I, I, I, I, F, D, I, P],
     "dk_sample": [P, I, I, I, P, P, P, P, P, P, P],
     "dk_attention_decode": [C.POINTER(AttnParams), P],
     "dk_attention_decode_supported": [I, I, I, I, I],

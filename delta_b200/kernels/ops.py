@@ -307,31 +307,34 @@ def gemm_stream_k(x, w, out, swiglu=False, err=None):
     return out
 
 
-def recent_pages(row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, ps, ratio):
+def recent_pages(row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, ps, ratio, page_ahead=False):
+    """``page_ahead``: a request whose newest page is exactly full counts one more, empty page (see delta_select.cu)."""
     i32 = torch.int32
     _l.check(_l.load().dk_recent_pages(_ptr(row_slot, "row_slot", i32), _ptr(row_flags, "row_flags", i32),
                                        _ptr(row_pos_start, "row_pos_start", i32), _ptr(row_q_len, "row_q_len", i32),
                                        _ptr(sel_pages, "sel_pages", i32), _ptr(sel_count, "sel_count", i32),
-                                       row_slot.shape[0], sel_pages.shape[1], ps, float(ratio), _stream()), "recent_pages")
+                                       row_slot.shape[0], sel_pages.shape[1], ps, float(ratio), int(page_ahead), _stream()), "recent_pages")
 
 
-def page_scores(dump, lse, row_flags, row_q_start, row_pos_start, row_q_len, scores, ps, k, ratio):
+def page_scores(dump, lse, row_flags, row_q_start, row_pos_start, row_q_len, scores, ps, k, ratio, page_ahead=False):
     rows, H, stride = dump.shape
     i32 = torch.int32
     _l.check(_l.load().dk_page_scores(_ptr(dump, "dump", torch.float32), _ptr(lse, "lse", torch.float32),
                                       _ptr(row_flags, "row_flags", i32), _ptr(row_q_start, "row_q_start", i32),
                                       _ptr(row_pos_start, "row_pos_start", i32), _ptr(row_q_len, "row_q_len", i32),
                                       _ptr(scores, "scores", torch.float32), rows, H, ps, stride, scores.shape[1], k,
-                                      float(ratio), _stream()), "page_scores")
+                                      float(ratio), int(page_ahead), _stream()), "page_scores")
 
 
-def select_pages(scores, row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, keep_last, ps, bias, ratio):
+def select_pages(scores, row_slot, row_flags, row_pos_start, row_q_len, sel_pages, sel_count, keep_last, ps, bias, ratio,
+                 page_ahead=False):
     i32 = torch.int32
     _l.check(_l.load().dk_select_pages(_ptr(scores, "scores", torch.float32), _ptr(row_slot, "row_slot", i32),
                                        _ptr(row_flags, "row_flags", i32), _ptr(row_pos_start, "row_pos_start", i32),
                                        _ptr(row_q_len, "row_q_len", i32), _ptr(sel_pages, "sel_pages", i32),
                                        _ptr(sel_count, "sel_count", i32), scores.shape[0], scores.shape[1],
-                                       sel_pages.shape[1], keep_last, ps, float(bias), float(ratio), _stream()), "select_pages")
+                                       sel_pages.shape[1], keep_last, ps, float(bias), float(ratio), int(page_ahead),
+                                       _stream()), "select_pages")
 
 
 def sample(logits, out, temperature=None, top_p=None, seeds=None, positions=None, err=None):

@@ -41,7 +41,8 @@ def yi_spec(cfg: YiConfig, engine: Optional[EngineConfig] = None) -> ModelSpec:
             role = sel.role(i, cfg.num_hidden_layers)
             if role != "full":
                 mixer.update(role=role, subset_cache_size=sel.subset_cache_size, keep_last=sel.keep_last,
-                             compression_ratio=sel.compression_ratio, position_bias=sel.position_bias)
+                             compression_ratio=sel.compression_ratio, position_bias=sel.position_bias,
+                             count_page_ahead=sel.count_page_ahead)
         layers.append(LayerSpec(dict(
             norm1=PartSpec("rms_norm", dict(name=pre + "input_layernorm.weight", width=d, eps=cfg.rms_norm_eps), "norm"),
             mixer=PartSpec("gqa_attention", mixer, "mixer"),

@@ -14,6 +14,8 @@ every new token attends causally to the keys of its request
   "subset"   decode rows read only the chosen pages (backend.py:486-516); before a
              planner has run in a step these are the most recent pages
              (backend.py:1871-1873).
+``count_page_ahead`` counts a request's pages as the reference's scheduler does (one more, empty, once
+the newest is exactly full); without it a request has the pages that hold its tokens.
 Rows of a prompt always read everything; the planner and subset roles apply to rows
 flagged ``ROW_DECODE`` (a single token at or after the prompt's end) of requests that hold
 more pages than the subset.  Which kernels run is chosen in ``attention_kernels``.
@@ -38,7 +40,7 @@ class GQAAttention(Mixer):
     def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, window: Optional[int] = None, role: str = "full",
                  subset_cache_size: int = 0, keep_last: int = 1, compression_ratio: float = 1.0,
-                 position_bias: float = 1e-7, scale: Optional[float] = None):
+                 position_bias: float = 1e-7, count_page_ahead: bool = False, scale: Optional[float] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} heads are no multiple of {kv_heads} key-value heads")
         if role not in ("full", "planner", "subset"):
@@ -55,6 +57,12 @@ class GQAAttention(Mixer):
         self.keep_last = int(keep_last)
         self.ratio = float(compression_ratio)
         self.bias = float(position_bias)
+        # the reference's count of a request's pages: one more, empty, once the newest is exactly full
+        # (DELTA/Engine/DELTA/scheduler.py:60-74); it takes a place among the chosen and is not read
+        self.page_ahead = bool(count_page_ahead)
+        if self.page_ahead and role != "full" and min(self.k, self.keep_last) < 2:
+            raise ValueError("with count_page_ahead the empty page takes one of the newest L places: L and subset_cache_size "
+                             "must be at least 2, or the page of the newest token would not be read")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.position = position.build(POSITION_ENCODINGS) if position is not None else None
         self.w_qkv = None
@@ -89,7 +97,7 @@ class GQAAttention(Mixer):
         if self.role == "full" or not ctx.any_row_flag(ROW_DECODE) or not ctx.once("delta.recent_pages"):
             return
         ops.recent_pages(ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
-                         ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), ctx.page_size, self.ratio)
+                         ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), ctx.page_size, self.ratio, self.page_ahead)
 
     def forward(self, ctx, x, cache):
         H, KV, hd = self.heads, self.kv_heads, self.head_dim
@@ -121,10 +129,10 @@ class GQAAttention(Mixer):
         if self.role == "planner" and selective:
             scores = ctx.scratch("delta.page_scores", (ctx.num_rows, ctx.max_pages), torch.float32, bound=(ctx.max_rows, widest))
             ops.page_scores(dump, lse, ctx.row_flags, ctx.row_q_start, ctx.row_pos_start, ctx.row_q_len, scores,
-                            cache.page_size, self.k, self.ratio)
+                            cache.page_size, self.k, self.ratio, self.page_ahead)
             ops.select_pages(scores, ctx.row_slot, ctx.row_flags, ctx.row_pos_start, ctx.row_q_len,
                              ctx.state(SELECTED_PAGES), ctx.state(SELECTED_COUNT), self.keep_last, cache.page_size,
-                             self.bias, self.ratio)
+                             self.bias, self.ratio, self.page_ahead)
             if ctx.capture is not None:
                 # for tests: what this planner chose, per (part, request slot, position)
                 pages, counts = ctx.state(SELECTED_PAGES).cpu(), ctx.state(SELECTED_COUNT).cpu()

@@ -3,6 +3,7 @@ random model, for the parts of it that need a GPU (rotary positions, the cache a
 the whole forward pass).  Run on a machine with a CUDA device, the reference on the path:
 
     PYTHONPATH=/path/to/hoenza-DELTA python tests/golden/make_reference_model_golden.py OUT.pt
+    PYTHONPATH=/path/to/hoenza-DELTA python tests/golden/make_reference_model_golden.py --selective OUT2.pt
 
 The reference's stock path is driven (tests/reasoni.py:320-342, 449-455): ``LMBackend`` ->
 ``load_model`` (a ``model.pth`` whose folder names the configuration; the tiny configuration is added
@@ -18,6 +19,12 @@ plain implementation, which reads the unconverted folder and rotates pairs (j, j
 the reference's logits, then half-split rotation on unconverted rows, the exponent of theta, the
 mapping of query heads to key-value heads, the placement of the norms and the untied output matrix
 are all what the reference computes.
+
+With ``--selective`` a second file is made, tests/golden/reference_selective_logits.pt: one request through
+the reference with DELTA on (three layers, ``full_cache_layers=[1]``: layer 0 reads the most recent pages,
+layer 1 plans, layer 2 reads the chosen pages; 4 pages of 16 tokens, the last 2 always kept), a prompt of 20
+tokens (fewer pages than the subset, so that the reference's prompt step reads everything, as the engine's
+always does) and 100 decoded tokens.
 
 tests/test_plain_against_reference.py compares the plain implementation with the stored logits.
 """
@@ -73,6 +80,61 @@ def to_reference_names(w, cfg):
         sd[q + "attention_norm.weight"] = w[p + "input_layernorm.weight"]
         sd[q + "ffn_norm.weight"] = w[p + "post_attention_layernorm.weight"]
     return {k: v.to(torch.bfloat16) for k, v in sd.items()}
+
+
+SEL_CONFIG = dict(CONFIG, num_hidden_layers=3)
+SEL = dict(full_cache_layers=[1], subset_cache_size=4, L=2, compression_ratio=1.0)
+SEL_PROMPT, SEL_NEW = 20, 100
+
+
+def main_selective(out_path):
+    import helpers
+    import plain_yi
+    from delta_b200.weights import write_random_model
+    import delta_b200.models  # noqa: F401
+    from DELTA.Engine.DELTA import model as ref_model
+    from DELTA.Engine.DELTA.backend import LMBackend
+    from DELTA.Engine.DELTA.public_config import FINAL_PUBLIC_DELTA_BACKEND_CONFIG
+
+    work = Path(tempfile.mkdtemp(prefix="golden_sel_"))
+    c = SEL_CONFIG
+    folder = write_random_model(work / "hf", c, SEED + 1, torch.float32)
+    w = plain_yi.read_safetensors_plain(folder / "model.safetensors")
+    name = NAME + "-selective"
+    ref_model.transformer_configs[name] = dict(block_size=c["max_position_embeddings"], n_layer=c["num_hidden_layers"],
+                                               n_head=c["num_attention_heads"], n_local_heads=c["num_key_value_heads"],
+                                               dim=c["hidden_size"], intermediate_size=c["intermediate_size"],
+                                               vocab_size=c["vocab_size"], rope_base=c["rope_theta"], norm_eps=c["rms_norm_eps"])
+    (work / name).mkdir()
+    torch.save(to_reference_names(w, c), str(work / name / "model.pth"))
+    eng = LMBackend(dtype=torch.bfloat16, device="cuda:0", cuda_graph_decode=False, **dict(FINAL_PUBLIC_DELTA_BACKEND_CONFIG))
+    eng.is_main_process = True
+    eng.load_model(work / name / "model.pth", use_tp=False, rank_group=[0], group=None)
+    cfg = eng.model.config                      # as tests/reasoni.py:327-335 sets them
+    cfg.enable_selective_cache = True
+    cfg.page_selector_version = FINAL_PUBLIC_DELTA_BACKEND_CONFIG["page_selector_version"]
+    cfg.page_selector_v2 = True
+    cfg.full_cache_layers = list(SEL["full_cache_layers"])
+    cfg.subset_cache_ratio = 0.5
+    cfg.compression_ratio = SEL["compression_ratio"]
+    cfg.subset_cache_size = SEL["subset_cache_size"]
+    cfg.L = SEL["L"]
+    eng.setup_caches(max_batch_size=1, max_seq_length=MAX_LEN)
+    steps = []
+    eng.model.output.register_forward_hook(lambda mod, inp, out: steps.append(out.detach().float().cpu().reshape(-1, out.shape[-1])))
+    prompt = torch.tensor(helpers.random_tokens(SEL_PROMPT, c["vocab_size"], 600))
+    eng.add_requests([prompt], [SEL_PROMPT + SEL_NEW], [])
+    eng.run_scheduler_loop()
+    out = list(map(int, eng.scheduler.request_queue[0].output_ids))
+    assert len(out) == SEL_NEW and steps[0].shape[0] == SEL_PROMPT and len(steps) == SEL_NEW
+    logits = torch.cat([steps[0]] + [s[:1] for s in steps[1:]])
+    assert logits.shape[0] == SEL_PROMPT + SEL_NEW - 1
+    assert out == [int(logits[SEL_PROMPT - 1 + j].argmax()) for j in range(SEL_NEW)]
+    golden = dict(config=c, seed=SEED + 1, weights_sha256=checksum(w), selective=SEL, page_size=16, prompt=prompt.tolist(),
+                  output=out, logits=logits.to(torch.bfloat16),
+                  made_with=dict(torch=str(torch.__version__), device=torch.cuda.get_device_name(0)))
+    torch.save(golden, out_path)
+    print(json.dumps(dict(written=str(out_path), output=out)))
 
 
 def main(out_path):
@@ -131,4 +193,7 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1])
+    if sys.argv[1] == "--selective":
+        main_selective(sys.argv[2])
+    else:
+        main(sys.argv[1])

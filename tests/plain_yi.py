@@ -237,6 +237,15 @@ class Selective:
     ratio: float = 1.0
     page_size: int = 16
     prompt_len: int = 0  # positions >= prompt_len are decode positions
+    # The reference's page accounting: a request whose length has just reached a multiple of the page size
+    # already holds the next, still empty page (DELTA/Engine/DELTA/scheduler.py:60-74), which counts among its
+    # pages in the selection.  The engine holds ceil(len / page_size) pages; this switch is for comparisons
+    # with outputs of the reference itself.
+    trailing_empty_page: bool = False
+
+    def pages_at(self, p: int) -> int:
+        """Pages the request counts when the token at position p is decoded."""
+        return (p + 1) // self.page_size + 1 if self.trailing_empty_page else p // self.page_size + 1
 
     def role(self, layer: int, n_layers: int) -> str:
         """full / planner / subset   (DELTA/Engine/DELTA/model.py:177-194)."""
@@ -307,7 +316,7 @@ class PlainYi:
         chosen = [None] * T
         if selective:
             for p in range(selective.prompt_len, T):
-                n = p // ps + 1
+                n = selective.pages_at(p)
                 if selection_active(n, selective.k, selective.ratio):
                     chosen[p] = recent_pages(n, selective.k)
         caches = {}
@@ -330,7 +339,7 @@ class PlainYi:
                 caches[cache_id] = kv
             if role == "planner":
                 for p in range(selective.prompt_len, T):
-                    n = p // ps + 1
+                    n = selective.pages_at(p)
                     if selection_active(n, selective.k, selective.ratio):
                         if forced is not None and (i, p) in forced:
                             # attend to the pages somebody else chose (a comparison in reduced precision,
@@ -338,6 +347,8 @@ class PlainYi:
                             chosen[p] = list(forced[(i, p)])
                             continue
                         sc = page_scores(s[:, p, :p + 1], p + 1, ps)
+                        if sc.shape[0] < n:      # the reference's empty trailing page: no keys, score zero
+                            sc = torch.cat([sc, sc.new_zeros(n - sc.shape[0])])
                         chosen[p] = select_pages(sc, n, selective.k, selective.L)
                         self.last_planned[(i, p)] = list(chosen[p])
         x = self._r(rms_norm(x, w["model.norm.weight"], c.eps, self.rnd))

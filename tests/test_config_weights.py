@@ -156,3 +156,11 @@ def test_spec_follows_config_layer_by_layer():
     for cid, cs in m.cache_specs().items():
         groups.setdefault(cs, []).append(cid)
     assert sorted(groups.values()) == [[0, 2], [1, 3]]
+
+
+def test_the_page_counted_ahead_needs_two_places():
+    from delta_b200.config import SelectiveCacheConfig
+    SelectiveCacheConfig(full_cache_layers=(0,), subset_cache_size=2, L=2, count_page_ahead=True)
+    for k, L in ((1, 2), (4, 1)):
+        with pytest.raises(ValueError, match="count_page_ahead"):
+            SelectiveCacheConfig(full_cache_layers=(0,), subset_cache_size=k, L=L, count_page_ahead=True)

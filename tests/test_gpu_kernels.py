@@ -637,6 +637,41 @@ def test_recent_pages_scores_and_selection():
             assert sel_count[s] == k and sel_pages[s].tolist() == want, (keep_last, b)
 
 
+def test_selection_with_the_page_counted_ahead():
+    """Requests whose newest page is exactly full count one more, empty page: it scores zero, takes a place
+    among the newest L, and is left out of the list; a request of the block table's full width (the
+    counted page would lie behind the table) and one with a partly filled page beside them."""
+    from plain_yi import select_pages as plain_select
+    o = ops()
+    ps, k, H, max_pages = 8, 4, 3, 16
+    seqs = [128, 64, 61, 40]          # 16 pages (+1 counted), 8 (+1), 8, 5 (+1)
+    B = len(seqs)
+    flags, slots = i32([1] * B), i32([2, 0, 3, 1])
+    pos_start, q_len, q_start = i32([n - 1 for n in seqs]), i32([1] * B), i32(list(range(B)))
+    sel_pages = torch.full((4, k), -7, dtype=torch.int32, device=DEV)
+    sel_count = torch.zeros(4, dtype=torch.int32, device=DEV)
+    o.recent_pages(slots, flags, pos_start, q_len, sel_pages, sel_count, ps, 1.0, page_ahead=True)
+    assert sel_count.tolist() == [k - 1, k - 1, k - 1, k]
+    assert sel_pages[2, :3].tolist() == [13, 14, 15] and sel_pages[0, :3].tolist() == [5, 6, 7]
+    assert sel_pages[3].tolist() == [4, 5, 6, 7] and sel_pages[1, :3].tolist() == [2, 3, 4]
+    z = torch.randn(B, H, max_pages * ps, device=DEV) * 2
+    lse = torch.stack([torch.logsumexp(z[b, :, :n], -1) for b, n in enumerate(seqs)])
+    scores = torch.full((B, max_pages), float("nan"), device=DEV)
+    o.page_scores(z, lse, flags, q_start, pos_start, q_len, scores, ps, k, 1.0, page_ahead=True)
+    for b, n in enumerate(seqs):
+        held = (n + ps - 1) // ps
+        assert not torch.isnan(scores[b, :held]).any() and torch.isnan(scores[b, held:]).all()
+    for keep_last in (2, 3, 4):
+        o.select_pages(scores, slots, flags, pos_start, q_len, sel_pages, sel_count, keep_last, ps, 1e-7, 1.0, page_ahead=True)
+        for b, n in enumerate(seqs):
+            held, counted = (n + ps - 1) // ps, n // ps + 1
+            sc = torch.cat([scores[b, :held].cpu(), torch.zeros(counted - held)])
+            want = [j for j in plain_select(sc, counted, k, keep_last) if j < held]
+            s = int(slots[b])
+            assert len(want) == k - (counted - held)
+            assert sel_count[s] == len(want) and sel_pages[s, :len(want)].tolist() == want, (keep_last, b)
+
+
 # ------------------------------------------------------------------ sampling
 
 def test_greedy_takes_the_lowest_index_among_equals():

@@ -117,3 +117,55 @@ def test_the_other_pairing_or_head_mapping_would_not_pass(reference_model):
             w = swapped.w[f"model.layers.{l}.self_attn.{name}.weight"]
             swapped.w[f"model.layers.{l}.self_attn.{name}.weight"] = w.view(c.kv_heads, c.head_dim, -1).flip(0).reshape(w.shape)
     assert (swapped.forward(prompt + out[:-1]) - ref).abs().max().item() > 0.04 * scale
+
+
+# ---- DELTA on: the newest pages, the page scores, the choice, and the reading of chosen pages ------
+
+@pytest.fixture(scope="module")
+def reference_selective(tmp_path_factory):
+    sys.path.insert(0, str(GOLDEN))
+    from make_reference_model_golden import checksum
+    from delta_b200.weights import write_random_model
+    import delta_b200.models  # noqa: F401
+    M = torch.load(GOLDEN / "reference_selective_logits.pt")
+    folder = write_random_model(tmp_path_factory.mktemp("golden_sel") / "hf", M["config"], M["seed"], torch.float32)
+    if checksum(P.read_safetensors_plain(folder / "model.safetensors")) != M["weights_sha256"]:
+        pytest.skip("this torch draws other random weights from the seed than the one the stored logits were made with")
+    return M, folder
+
+
+def selective_of(M, **more):
+    s = M["selective"]
+    return P.Selective(full_layers=tuple(s["full_cache_layers"]), k=s["subset_cache_size"], L=s["L"], ratio=s["compression_ratio"],
+                       page_size=M["page_size"], prompt_len=len(M["prompt"]), **more)
+
+
+def test_selective_logits_equal_the_reference(reference_selective):
+    """The reference ran one request of 20 prompt tokens and 100 decoded ones with DELTA on: three layers,
+    layer 0 reads the newest 4 pages, layer 1 scores and chooses 4 pages (the newest 2 always), layer 2 reads
+    them.  With the reference's count of pages the plain implementation agrees at all 119 positions to the
+    rounding of bfloat16 (1.0 % of the largest logit is the worst seen; the bound is 1.5 %)."""
+    M, folder = reference_selective
+    ref = M["logits"].float()
+    seq = M["prompt"] + M["output"][:-1]
+    plain = P.PlainYi(folder, rounding="bfloat16")
+    got = plain.forward(seq, selective_of(M, trailing_empty_page=True))
+    scale = ref.abs().max().item()
+    err = (got - ref).abs().amax(dim=-1)
+    assert err.max().item() <= 0.015 * scale, f"position {int(err.argmax())} differs by {err.max().item():.4f} (largest logit {scale:.3f})"
+    assert len(plain.last_planned) >= 50          # the choice was made at more than half of the decoded positions
+
+
+def test_what_the_selective_comparison_sees(reference_selective):
+    """Reading everything instead of the chosen pages misses the stored logits by a quarter of the largest one;
+    counting only the pages that hold tokens differs where a page has just filled, and only from there on."""
+    M, folder = reference_selective
+    ref = M["logits"].float()
+    seq = M["prompt"] + M["output"][:-1]
+    scale = ref.abs().max().item()
+    plain = P.PlainYi(folder, rounding="bfloat16")
+    everything = (plain.forward(seq) - ref).abs().amax(dim=-1) / scale
+    assert everything.max().item() > 0.25
+    own = (plain.forward(seq, selective_of(M)) - ref).abs().amax(dim=-1) / scale
+    first = int((own > 0.015).nonzero()[0])
+    assert own.max().item() > 0.05 and (first + 1) % M["page_size"] == 0
