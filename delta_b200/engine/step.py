@@ -13,6 +13,7 @@ copy to the device.
 """
 from __future__ import annotations
 
+import gc
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -353,6 +354,12 @@ class ModelRunner:
             # two eager runs have sized the working buffers; now record the same launches
             torch.cuda.synchronize()
             l0 = ops.launch_count()
+            # No garbage collection while the stream records: a collected object that frees something of
+            # CUDA's (the graphs of an engine that is no longer used, say) makes calls that are not allowed
+            # during a recording and would spoil it.  What is garbage now is collected before.
+            gc_was_on = gc.isenabled()
+            gc.collect()
+            gc.disable()
             try:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
@@ -361,9 +368,13 @@ class ModelRunner:
                 g["launches"] = ops.launch_count() - l0     # kernels recorded, not run
                 self.graph_captures += 1
             except Exception as e:  # noqa: BLE001  (whatever stops the recording: this size stays eager)
-                g["failed"] = f"capture failed: {type(e).__name__}"
+                first = (str(e).strip().splitlines() or [""])[0][:160]
+                g["failed"] = f"capture failed: {type(e).__name__}: {first}"
                 g["error"] = str(e)
                 torch.cuda.synchronize()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             ops.count_launch(l0 - ops.launch_count())
         if g["graph"] is None:
             g["warm"] += 1

@@ -302,3 +302,46 @@ def test_a_failed_graph_recording_falls_back_to_eager_steps(model_folders, monke
     assert e.runner.graph_captures == 0 and e.runner.graph_replays == 0
     assert sum(e.runner.graph_fallbacks.values()) >= 8 and all("capture failed" in k for k in e.runner.graph_fallbacks)
     assert "refused" in e.runner._graphs[3]["error"]
+
+
+def test_garbage_of_an_earlier_engine_does_not_spoil_a_recording(model_folders):
+    """An engine that is no longer used, with its CUDA graphs, may lie in a reference cycle until Python's
+    garbage collector meets it.  If that happens while a later engine records a decode step, freeing the
+    old graphs is a call that CUDA does not allow during a recording, and the recording is lost.  Here the
+    old engine becomes garbage in the middle of the second engine's recording and a collection follows at
+    once if the collector is enabled at that moment (which is when an automatic collection could run; when
+    one really runs depends on Python's counts of objects); the second engine must still record."""
+    import gc
+    from delta_b200.engine import LMBackend
+    folder = model_folders["A"]
+    vocab = PlainYi(folder).cfg.vocab
+    prompts = [helpers.random_tokens(n, vocab, 650 + i) for i, n in enumerate([12, 30, 7])]
+
+    def engine():
+        e = LMBackend(dtype="float32", device="cuda:0", cuda_graph_decode=True)
+        e.load_model(folder)
+        e.setup_caches(max_batch_size=3, max_seq_length=64, page_size=16)
+        return e
+
+    old = engine()
+    want = old.generate(prompts, 12)
+    assert old.runner.graph_captures >= 1
+    cycle = [old]
+    cycle.append(cycle)
+    box = {"old": cycle}
+    del old, cycle
+    e = engine()
+    forward = e.runner.model.forward
+    dropped = []
+
+    def forward_that_drops_the_old_engine(ctx):
+        if box and torch.cuda.is_current_stream_capturing():
+            box.clear()                   # from here on only the collector can free the old engine
+            dropped.append(gc.isenabled())
+            if gc.isenabled():
+                gc.collect()
+        return forward(ctx)
+    e.runner.model.forward = forward_that_drops_the_old_engine
+    got = e.generate(prompts, 12)
+    assert not e.runner.graph_fallbacks and e.runner.graph_captures >= 1
+    assert dropped == [False] and got == want
