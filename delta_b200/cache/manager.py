@@ -51,7 +51,7 @@ class CacheGroup:
                  max_slots: int, max_pages_per_request: int, dtype, device, shuffle_seed=None):
         self.name, self.spec, self.cache_ids = name, spec, list(cache_ids)
         self.page_size = page_size
-        self.pool = PagePool(num_pages, shuffle_seed)
+        self.pool = PagePool(num_pages, shuffle_seed, run_pages=max(1, spec.run_tokens // page_size))
         self.index_of = {cid: i for i, cid in enumerate(self.cache_ids)}
         # one page more than the pool hands out: the spare page that the padding slot points at
         self.pages = torch.zeros((len(self.cache_ids), num_pages + 1, *spec.page_shape(page_size)), dtype=dtype, device=device)
@@ -170,8 +170,9 @@ class CacheManager:
                 raise OutOfPages(f"out of cache pages in group {n}: {need[n]} needed, {g.pool.free_pages} free")
         for n, g in self.groups.items():
             if need[n]:
-                pages = g.pool.alloc(need[n])
                 a = int(g.num_logical[slot])
+                last = int(g.table[slot, a - 1]) if a > 0 else -1
+                pages = g.pool.alloc(need[n], after=last if last >= 0 else None)
                 g.table[slot, a:a + need[n]] = pages
                 g.num_logical[slot] = a + need[n]
 

@@ -129,15 +129,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
     return;
   }
 
-  // this block's share of the pages
-  const int per = (ri.n_entries + p.splits - 1) / p.splits;
+  // this block's share of the pages: whole tiles, so that tiles begin where the pool's runs of pages begin
+  const int pages_per_tile = TILE / ps;
+  const int per = ((ri.n_entries + p.splits - 1) / p.splits + pages_per_tile - 1) / pages_per_tile * pages_per_tile;
   if (per > p.block_entries) {  // more pages than the block table is wide: a wrong table, not a case to compute
     if (tid == 0) dk_report(p.err, DK_DEV_BAD_POSITION, ri.t, ri.pos, p.max_pages * p.ps);
     return;
   }
   const int e_begin = split * per;
   const int e_end = min(ri.n_entries, e_begin + per);
-  const int pages_per_tile = TILE / ps;
   const int n_tiles = e_end > e_begin ? (e_end - e_begin + pages_per_tile - 1) / pages_per_tile : 0;
 
   // this block's pages: logical and physical ids, looked up once
@@ -578,8 +578,9 @@ int configure(size_t smem) {
 template <int HD, bool LOW, bool TMA>
 int launch(const DkAttnParams& pin, cudaStream_t stream) {
   DkAttnParams p = pin;
-  // entries (pages) one block can be given: the widest request split evenly
-  p.block_entries = (p.max_pages + p.splits - 1) / p.splits;
+  // entries (pages) one block can be given: the widest request split evenly, in whole tiles
+  const int pages_per_tile = TILE / p.ps > 0 ? TILE / p.ps : 1;
+  p.block_entries = ((p.max_pages + p.splits - 1) / p.splits + pages_per_tile - 1) / pages_per_tile * pages_per_tile;
   if (p.block_entries > 8192) {
     dk_set_error("attention_decode: %d pages per block are above the 8192 it keeps in shared memory; use more splits", p.block_entries);
     return DK_ERR_ARG;

@@ -82,7 +82,8 @@ class GQAAttention(Mixer):
 
     def cache_spec(self):
         # a page of a layer: [K|V][kv head][offset in the page][head_dim]
-        return CacheSpec((2, self.kv_heads, PAGE, self.head_dim), self.window)
+        # (the kernels fetch a tile of keys whose pages follow one another with one copy; the widest tile has 128 keys)
+        return CacheSpec((2, self.kv_heads, PAGE, self.head_dim), self.window, run_tokens=128)
 
     def decode_rows_differ(self):
         return self.role != "full"

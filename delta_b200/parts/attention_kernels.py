@@ -74,7 +74,8 @@ def _decode(ctx, params, row_filter: int, group: str) -> None:
     # ask for the occupancy without them, split, and ask again with what a block then holds
     per_sm = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, 0)
     splits = decode_splits(rows, params.KV, max_keys, ctx.sm_count, per_sm)
-    held = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, -(-params.max_pages // splits))
+    tile_pages = max(1, DECODE_TILE // params.ps)           # a block's share is a whole number of tiles
+    held = ops.attention_decode_blocks_per_sm(params.H, params.KV, params.hd, -(-(-(-params.max_pages // splits)) // tile_pages) * tile_pages)
     if held < per_sm:
         per_sm = held
         splits = decode_splits(rows, params.KV, max_keys, ctx.sm_count, per_sm)

@@ -51,9 +51,13 @@ class CacheSpec:
     manager allocates ``[layers of the group, pages, *layout]`` with the page size
     in place of ``PAGE`` and knows nothing else about the contents.  Mixers with
     equal specs share a cache group (one pool of pages, one block table per
-    request); ``window`` None means every token is kept."""
+    request); ``window`` None means every token is kept.  ``run_tokens``: the mixer reads
+    a request's pages fastest when the pages of this many consecutive tokens follow one another
+    in the pool; the pool then hands pages out in aligned runs of that length where it can
+    (0: any order is as good)."""
     layout: tuple
     window: Optional[int] = None
+    run_tokens: int = 0
 
     def __post_init__(self):
         if tuple(self.layout).count(PAGE) != 1:

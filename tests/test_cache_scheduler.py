@@ -36,6 +36,68 @@ def test_pool_is_lifo_and_strict():
     assert sorted(PagePool(8, shuffle_seed=0).alloc(8)) == list(range(8))
 
 
+def test_pool_hands_out_runs():
+    """Requests that grow by one page in turns still hold aligned runs; many pages at once come in order;
+    runs given back are used again first, in their order; when no run is wholly free, pages of begun runs
+    are taken, and every free page can be had."""
+    R = 4
+    p = PagePool(128, run_pages=R)
+    held = {r: [] for r in range(5)}
+    for _ in range(9):                                   # five requests, a page each in turn, nine times
+        for r in held:
+            held[r] += p.alloc(1, after=held[r][-1] if held[r] else None)
+    for r, pages in held.items():
+        for j in range(0, 8, R):                         # the first two runs of every request
+            assert pages[j] % R == 0 and pages[j:j + R] == list(range(pages[j], pages[j] + R)), (r, pages)
+    p.check()
+    big = p.alloc(10, after=None)
+    assert big == list(range(big[0], big[0] + 10)) and big[0] % R == 0
+    # request 1 ends: its runs come back and are the next ones handed out, in their order
+    p.free(held[1])
+    again = p.alloc(8)
+    assert again == held[1][:8]
+    p.check()
+    # use the pool up: pages of begun runs are handed out too, down to the last page
+    rest = p.alloc(p.free_pages)
+    assert p.free_pages == 0 and len(set(rest)) == len(rest)
+    with pytest.raises(OutOfPages):
+        p.alloc(1)
+    p.check()
+    # a pool whose size is no multiple of the run
+    q = PagePool(10, run_pages=4)
+    assert q.alloc(10) == list(range(10))
+    q.free([9, 8])
+    assert q.alloc(2, after=7) == [8, 9]
+    q.check()
+
+
+def test_pool_under_random_orders_with_runs():
+    rng = random.Random(5)
+    for R, n in ((1, 13), (4, 30), (8, 64), (8, 21)):
+        p = PagePool(n, run_pages=R)
+        held = {}
+        for step in range(600):
+            if held and (rng.random() < 0.45 or p.free_pages == 0):
+                r = rng.choice(list(held))
+                k = rng.randint(1, len(held[r]))
+                if rng.random() < 0.5:
+                    gone, held[r] = held[r][:k], held[r][k:]       # a window passes the oldest pages
+                else:
+                    gone, held[r] = held[r], []
+                p.free(gone)
+                if not held[r]:
+                    del held[r]
+            else:
+                r = rng.randint(0, 5)
+                k = rng.randint(1, min(6, p.free_pages))
+                got = p.alloc(k, after=held[r][-1] if held.get(r) else None)
+                assert len(got) == k
+                held.setdefault(r, []).extend(got)
+            everything = [x for v in held.values() for x in v]
+            assert len(set(everything)) == len(everything) == p.held_pages
+            p.check()
+
+
 def test_grow_release_reuse():
     m = manager(num_pages=6)
     s = m.acquire_slot()
@@ -55,6 +117,25 @@ def test_grow_release_reuse():
     assert set(m.groups["2x2xPx8"].held(t)) == set(held)   # pages are used again
     with pytest.raises(ValueError, match="twice"):
         m.release_slot(s)
+    m.check()
+
+
+def test_requests_that_grow_in_turns_hold_runs_of_pages():
+    """Six requests decode in turns, a token each; with a mixer that asks for runs of 8 tokens' pages (two
+    pages of 4) every request's block table is made of aligned pairs of pages that follow one another."""
+    specs = {0: CacheSpec((2, 2, PAGE, 8), run_tokens=8)}
+    m = CacheManager(specs, {}, max_slots=6, max_seq_len=64, page_size=4, num_pages=96, dtype=torch.float32, device="cpu")
+    slots = [m.acquire_slot() for _ in range(6)]
+    for n in range(1, 41):
+        for s in slots:
+            m.grow(s, n)
+            m.advance(s, n)
+    g = m.groups["2x2xPx8"]
+    for s in slots:
+        pages = g.held(s)
+        assert len(pages) == 10
+        for j in range(0, 10, 2):
+            assert pages[j] % 2 == 0 and pages[j + 1] == pages[j] + 1, pages
     m.check()
 
 
