@@ -40,6 +40,9 @@ Other workloads (``--workload``), each printing one JSON line of the same shape:
   yi34b-mixed  Yi-34B shape: steps of one 2,048-token prompt portion beside up to 63 decoding
                requests; milliseconds per mixed step, tokens per second of both kinds, and the
                portion's share of the tensor-core peak
+  grown        Yi-6B shape, 64 requests (``--batch``) of 64 + 2,400 tokens: nearly every page is taken
+               during decoding, a page at a time in turns with the other requests; the last sixth of
+               the decode steps, with the pool handing pages out in runs and one by one
 
 ``--impl reference`` runs the unmodified hoenza/DELTA engine (baseline/reference_arm.py) on the
 default workload and prints its line.
@@ -211,7 +214,7 @@ def other_workload(args) -> int:
     pk = peaks()
     gen = torch.Generator().manual_seed(1)
     name = args.workload
-    shape = {"baseline": "yi-6b", "yi9b-long": "yi-9b", "yi34b-mixed": "yi-34b"}[name]
+    shape = {"baseline": "yi-6b", "yi9b-long": "yi-9b", "yi34b-mixed": "yi-34b", "grown": "yi-6b"}[name]
     shape_name, shape_cfg = SHAPES[shape]
     layers = args.layers or shape_cfg["num_hidden_layers"]
     cfg = dict(shape_cfg, num_hidden_layers=layers)
@@ -280,6 +283,32 @@ def other_workload(args) -> int:
                                       generated=new, full_cache_layers="2", subset_cache_size=64, cuda_graph_decode=not args.no_graph),
                "full_cache": res["full"], "delta": res["delta"],
                "delta_over_full": res["delta"]["tokens_per_s"] / res["full"]["tokens_per_s"], "clocks": clk}
+    elif name == "grown":
+        # Many requests with short prompts that decode for a long time, in turns: nearly every page of a request
+        # is taken during decoding, one at a time, between the pages the other requests take.  Measured with the
+        # pool handing out runs of pages, and with the one-page last-in-first-out stack.
+        B, plen, new = args.batch if args.batch != 8 else 64, 64, args.generate or 2400
+        res = {}
+        clocks.start()
+        for runs in (True, False):
+            eng = engine(B, plen + new, max_tokens_per_step=4096, page_runs=runs)
+            _loop(eng, prompts(B, plen), 24, True)
+            decode, _ = _loop(eng, prompts(B, plen), new, True)
+            tail = decode[-max(1, len(decode) // 6):]
+            res[runs] = sum(r["model_forward_ms"] + r["postprocess_ms"] for r in tail) / len(tail)
+            del eng
+            torch.cuda.empty_cache()
+        clk = clocks.stop()
+        ctx = plen + new * 11 / 12
+        achieved = (weight_bytes + B * ctx * kv_per_tok) / (res[True] / 1e3) / 1e9
+        out = {"workload": name, "metric": f"decode tok/s ({shape_name}, bf16, batch {B}, {plen}-token prompts + {new} generated, last sixth of the steps)",
+               "value": B / (res[True] / 1e3), "unit": "tokens/s", "n_gpus": 1, "ms_per_step": res[True], "higher_is_better": True,
+               "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+               "config": _flat_config(shape_name, shape_cfg, layers, global_batch=B, seq_len=plen + new, prompt_len=plen, generated=new,
+                                      cuda_graph_decode=not args.no_graph, peaks=pk["source"]),
+               "ms_per_step_pages_in_runs": res[True], "ms_per_step_pages_one_by_one": res[False],
+               "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+               "clocks": clk}
     else:
         B, portion, ctx_len = 64, 2048, 4096
         eng = engine(B, ctx_len, max_tokens_per_step=portion + B)
@@ -331,7 +360,7 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed"], default="decode")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown"], default="decode")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -48,10 +48,10 @@ class LayerCacheView:
 
 class CacheGroup:
     def __init__(self, name: str, spec: CacheSpec, cache_ids: List[int], num_pages: int, page_size: int,
-                 max_slots: int, max_pages_per_request: int, dtype, device, shuffle_seed=None):
+                 max_slots: int, max_pages_per_request: int, dtype, device, shuffle_seed=None, page_runs=True):
         self.name, self.spec, self.cache_ids = name, spec, list(cache_ids)
         self.page_size = page_size
-        self.pool = PagePool(num_pages, shuffle_seed, run_pages=max(1, spec.run_tokens // page_size))
+        self.pool = PagePool(num_pages, shuffle_seed, run_pages=max(1, spec.run_tokens // page_size) if page_runs else 1)
         self.index_of = {cid: i for i, cid in enumerate(self.cache_ids)}
         # one page more than the pool hands out: the spare page that the padding slot points at
         self.pages = torch.zeros((len(self.cache_ids), num_pages + 1, *spec.page_shape(page_size)), dtype=dtype, device=device)
@@ -84,7 +84,8 @@ class CacheManager:
     they read and write nothing that belongs to a request."""
 
     def __init__(self, cache_specs: Dict[int, CacheSpec], state_specs: Dict[str, StateSpec], *, max_slots: int,
-                 max_seq_len: int, page_size: int, num_pages, dtype=torch.bfloat16, device="cuda", shuffle_seed=None):
+                 max_seq_len: int, page_size: int, num_pages, dtype=torch.bfloat16, device="cuda", shuffle_seed=None,
+                 page_runs: bool = True):
         self.max_slots, self.max_seq_len, self.page_size = int(max_slots), int(max_seq_len), int(page_size)
         self.max_pages_per_request = (self.max_seq_len + page_size - 1) // page_size
         self.device = device
@@ -96,7 +97,8 @@ class CacheManager:
         for spec, cids in by_spec.items():
             name = spec.describe()
             n = num_pages[name] if isinstance(num_pages, dict) else int(num_pages)
-            g = CacheGroup(name, spec, cids, n, page_size, self.max_slots, self.max_pages_per_request, dtype, device, shuffle_seed)
+            g = CacheGroup(name, spec, cids, n, page_size, self.max_slots, self.max_pages_per_request, dtype, device, shuffle_seed,
+                           page_runs)
             self.groups[name] = g
             for cid in cids:
                 self.group_of_cache[cid] = g

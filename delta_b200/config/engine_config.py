@@ -30,6 +30,7 @@ class EngineConfig:
     cuda_graph_decode: bool = False
     check_kernel_errors: bool = True   # read the kernels' error record with every step's result
     shuffle_pages: Optional[int] = None  # seed: hand pages out in a shuffled order
+    page_runs: bool = True               # hand pages out in the runs a mixer asks for (False: one page at a time, last in first out)
     options: Mapping[str, Any] = field(default_factory=dict)   # for the architecture's specification builder
 
     def __post_init__(self):

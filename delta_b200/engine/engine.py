@@ -81,7 +81,7 @@ class LMBackend:
                      enable_selective_cache: Optional[bool] = None, full_cache_layers=None,
                      subset_cache_size: Optional[int] = None, compression_ratio: Optional[float] = None,
                      L: Optional[int] = None, count_page_ahead: Optional[bool] = None, check_kernel_errors: bool = True, rope_interleaved: bool = False,
-                     shuffle_pages: Optional[int] = None):
+                     shuffle_pages: Optional[int] = None, page_runs: bool = True):
         """``check_kernel_errors``: the kernels' error record (a bad page id, token id or position
         that a kernel skipped, a wait inside a kernel that ran out) travels to the host with every
         step's tokens and raises there; this costs no synchronisation."""
@@ -106,7 +106,7 @@ class LMBackend:
         cfg = EngineConfig(max_batch=max_batch_size, max_seq_len=max_seq_length, page_size=page_size, num_pages=num_pages,
                            dtype=self.dtype, max_tokens_per_step=max_tokens_per_step,
                            cuda_graph_decode=self.cuda_graph_decode, check_kernel_errors=check_kernel_errors,
-                           shuffle_pages=shuffle_pages,
+                           shuffle_pages=shuffle_pages, page_runs=page_runs,
                            options=dict(selective_cache=selective, rope_interleaved=rope_interleaved))
         self.engine_config = cfg
         self.runner = ModelRunner(self._model_dir, engine_config=cfg, config_json=self._config_json, seed=self._seed,

@@ -104,7 +104,7 @@ class ModelRunner:
         self.cache = CacheManager(self.model.cache_specs(), self.model.state_specs(), max_slots=self.cfg.max_batch,
                                   max_seq_len=self.cfg.max_seq_len, page_size=self.cfg.page_size,
                                   num_pages=self.cfg.pool_pages, dtype=self.dtype, device=self.device,
-                                  shuffle_seed=self.cfg.shuffle_pages)
+                                  shuffle_seed=self.cfg.shuffle_pages, page_runs=self.cfg.page_runs)
         self.vocab_size = self.spec.vocab_size
         self.err = ops.new_error_record(self.device)
         self._scratch: Dict[str, torch.Tensor] = {}
