@@ -9,7 +9,12 @@
 // mma.sync.m16n8k16 (rows = the G <= 16 query heads of the group), an online softmax
 // in float on its own keys, then O += P V.  The four warps are merged through shared
 // memory at the end; with more than one split the block writes (m, l, O) to the
-// scratch buffer and a second kernel merges the splits in a fixed order.
+// scratch buffer and a second kernel merges the splits in a fixed order.  With two to
+// eight splits the blocks of one (row, key-value head) can instead be launched as one
+// thread-block cluster: each keeps (m, l, O) in its own shared memory, and after a
+// cluster barrier block r merges the r-th share of the output columns from all of them
+// over distributed shared memory, in the same order with the same arithmetic, so that
+// neither the scratch buffer nor the second kernel is needed.
 //
 // The kernel is bound by the bytes of K and V it has to read once; the tensor-core
 // work is small beside it, which is why the legacy warp-level MMA is enough here.
@@ -30,6 +35,9 @@
 #include "attention_params.h"
 #include "mma_helpers.cuh"
 #include "tcgen05_helpers.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int TILE = 64;     // keys per tile
@@ -120,6 +128,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
   if (TMA && tid == 0)   // the descriptor is on its way while the pages are looked up
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_run)) : "memory");
   const int G = p.H / p.KV, ps = p.ps;
+  // (reserved bit 1) the splits of this (row, key-value head) are one cluster and merge among themselves.  Every way out
+  // of the kernel before the cluster's barriers is taken by all blocks of a cluster or by none: they depend on the row alone.
+  const bool cluster_merge = (p.reserved & 2) != 0 && p.splits > 1;
   if (p.row_filter == 1 && p.row_q_len[row] != 1) return;   // a row of a prompt: the prefill kernel's
   const RowInfo ri = row_info(p, row);
   const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(p.kv);
@@ -345,7 +356,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
       }
       if (TMA && s_timeout) {      // somebody's wait ran out (written before the barrier above): nothing is stored
         if (tid == 0) dk_report(p.err, DK_DEV_TIMEOUT, row, kvh, split);
-        return;
+        if (!cluster_merge) return;
+        break;                     // in a cluster the others wait for this block at the barriers: the error is recorded, the output is not to be used
       }
       const int nxt = tile + STAGES - 1;
       issued_ok = true;
@@ -463,6 +475,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
   float* w_o = reinterpret_cast<float*>(smem);         // [NWARPS][16][HD]
   float* w_m = w_o + NWARPS * 16 * HD;                 // [NWARPS][16]
   float* w_l = w_m + NWARPS * 16;                      // [NWARPS][16]
+  float* c_o = w_l + NWARPS * 16;                      // cluster merge: this block's [G][HD] output, then {m, l} per row
+  float* c_ml = c_o + 16 * HD;
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
     float* base = w_o + ((size_t)warp * 16) * HD + n * 8 + 2 * tq;
@@ -499,7 +513,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
     if (p.splits == 1) {
       reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)ri.t * p.H * HD + (size_t)h * HD + d] =
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-      if (p.lse != nullptr && d == 0) p.lse[(size_t)ri.t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
+      if (p.lse != nullptr && d == 0) p.lse[(size_t)ri.t * p.H + h] = L > 0.f ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
+    } else if (cluster_merge) {
+      c_o[idx] = acc;
+      if (d == 0) {
+        c_ml[2 * r] = M;
+        c_ml[2 * r + 1] = L;
+      }
     } else {
       float* sc = reinterpret_cast<float*>(p.scratch);
       sc[part_o_index(p, row, h, split, HD) + d] = acc;
@@ -508,6 +528,49 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_decode_kernel(const __g
         sc[part_ml_index(p, row, h, split) + 1] = L;
       }
     }
+  }
+  if (cluster_merge) {
+    // Block `split` of the cluster merges its share of the [G][HD] outputs from all blocks' shared memory, in split
+    // order and with the arithmetic of the merge kernel below (so both ways give the same bits).
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int S = p.splits;                 // 2..8, the cluster's size
+    const int total = G * HD;
+    const int share = (total + S - 1) / S;
+    const int end = min(total, (split + 1) * share);
+    const float* ro[8];
+    const float* rml[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ro[j] = j < S ? cluster.map_shared_rank(c_o, j) : c_o;
+      rml[j] = j < S ? cluster.map_shared_rank(c_ml, j) : c_ml;
+    }
+    for (int idx = split * share + tid; idx < end; idx += NTHREADS) {
+      const int r = idx / HD, d = idx % HD;
+      float m[8], l[8], o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool ok = j < S;
+        m[j] = ok ? rml[j][2 * r] : -INFINITY;
+        l[j] = ok ? rml[j][2 * r + 1] : 0.f;
+        o[j] = ok ? ro[j][idx] : 0.f;
+      }
+      float M = -INFINITY, L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) M = fmaxf(M, m[j]);
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = m[j] == -INFINITY ? 0.f : exp2f(m[j] - M);
+          L += l[j] * f;
+          acc += o[j] * f;
+        }
+      }
+      const int h = kvh * G + r;
+      reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)ri.t * p.H * HD + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      if (p.lse != nullptr && d == 0) p.lse[(size_t)ri.t * p.H + h] = L > 0.f ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
+    }
+    cluster.sync();                           // nobody leaves while its shared memory is still read
   }
 }
 
@@ -553,7 +616,7 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
   }
   if (d < HD)
     reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)t * p.H * HD + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-  if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? (M * 0.6931471805599453f + logf(L)) : -INFINITY;
+  if (p.lse != nullptr && d == 0) p.lse[(size_t)t * p.H + h] = L > 0.f ? fmaf(M, 0.6931471805599453f, logf(L)) : -INFINITY;
 }
 
 // Raises the kernel's limit of dynamic shared memory to ``smem`` bytes on the current device when it is
@@ -586,7 +649,7 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
     return DK_ERR_ARG;
   }
   const size_t tile_bytes = (size_t)STAGES * 2 * TILE * HD * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)3 * p.block_entries * sizeof(int);
-  constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
+  constexpr size_t merge_bytes = (size_t)NWARPS * 16 * HD * sizeof(float) + 2 * NWARPS * 16 * sizeof(float) + (size_t)16 * HD * sizeof(float) + 32 * sizeof(float);
   const size_t smem = (tile_bytes > merge_bytes ? tile_bytes : merge_bytes) + (TMA ? 1024 : 0);
   CUtensorMap map_run;
   memset(&map_run, 0, sizeof(map_run));
@@ -601,6 +664,27 @@ int launch(const DkAttnParams& pin, cudaStream_t stream) {
   }
   if (int rc = configure<HD, LOW, TMA>(smem)) return rc;
   dim3 grid(p.splits, p.KV, p.rows);
+  if ((p.reserved & 2) != 0 && p.splits > 1) {
+    // the splits of a (row, key-value head) as one cluster, which merges them itself
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, LOW, TMA>, map_run, p);
+    if (e != cudaSuccess) {
+      dk_set_error("attention_decode: launch of clusters of %d blocks failed: %s", p.splits, cudaGetErrorString(e));
+      return DK_ERR_LAUNCH;
+    }
+    return dk_check_launch("attention_decode");
+  }
   attention_decode_kernel<HD, LOW, TMA><<<grid, NTHREADS, smem, stream>>>(map_run, p);
   int rc = dk_check_launch("attention_decode");
   if (rc != 0 || p.splits == 1) return rc;
@@ -621,7 +705,7 @@ extern "C" long long dk_attention_decode_scratch_floats(int rows, int H, int hd,
 extern "C" int dk_attention_decode_blocks_per_sm(int H, int KV, int hd, int block_entries) {
   if (KV <= 0 || (hd != 64 && hd != 128)) return 0;
   const size_t tile_bytes = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)3 * block_entries * sizeof(int);
-  const size_t merge_bytes = (size_t)NWARPS * 16 * hd * sizeof(float) + 2 * NWARPS * 16 * sizeof(float);
+  const size_t merge_bytes = (size_t)NWARPS * 16 * hd * sizeof(float) + 2 * NWARPS * 16 * sizeof(float) + (size_t)16 * hd * sizeof(float) + 32 * sizeof(float);
   const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
   const bool low = H / KV <= 8;
   int n = 0, rc;
@@ -647,6 +731,48 @@ extern "C" int dk_attention_decode_blocks_per_sm(int H, int KV, int hd, int bloc
   return n;
 }
 
+// Clusters of ``splits`` blocks of the decode kernel that the device holds at once (a cluster needs all its blocks
+// resident in one GPC at the same time, so this is less than blocks per SM x SMs / splits); 0 with the error set on failure.
+extern "C" int dk_attention_decode_max_clusters(int H, int KV, int hd, int block_entries, int splits) {
+  if (KV <= 0 || (hd != 64 && hd != 128) || splits < 1 || splits > 8) return 0;
+  const size_t tile_bytes = (size_t)STAGES * 2 * TILE * hd * 2 + (size_t)STAGES * TILE * sizeof(int) + (size_t)3 * block_entries * sizeof(int);
+  const size_t merge_bytes = (size_t)NWARPS * 16 * hd * sizeof(float) + 2 * NWARPS * 16 * sizeof(float) + (size_t)16 * hd * sizeof(float) + 32 * sizeof(float);
+  const size_t smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+  const bool low = H / KV <= 8;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, 1, 1);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0, rc;
+  cudaError_t e;
+  if (hd == 64 && low) {
+    rc = configure<64, true, false>(smem);
+    e = cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<64, true, false>, &cfg);
+  } else if (hd == 64) {
+    rc = configure<64, false, false>(smem);
+    e = cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<64, false, false>, &cfg);
+  } else if (low) {
+    rc = configure<128, true, false>(smem);
+    e = cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<128, true, false>, &cfg);
+  } else {
+    rc = configure<128, false, false>(smem);
+    e = cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<128, false, false>, &cfg);
+  }
+  if (rc != 0) return 0;
+  if (e != cudaSuccess) {
+    dk_set_error("attention_decode: cluster occupancy query failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  return n;
+}
+
 // 1 when the fast kernel takes these sizes, else 0 (the caller then uses the plain kernel).
 extern "C" int dk_attention_decode_supported(int dtype, int H, int KV, int hd, int ps) {
   if (dtype != DK_BF16 || KV <= 0 || H % KV != 0) return 0;
@@ -666,7 +792,8 @@ extern "C" int dk_attention_decode(const DkAttnParams* pp, cudaStream_t stream) 
              "attention_decode: %d tokens for %d rows; every row must bring one token unless rows are filtered", p.T, p.rows);
   DK_REQUIRE(p.row_q_start != nullptr && p.row_q_len != nullptr, "attention_decode: row_q_start / row_q_len are missing");
   DK_REQUIRE(p.splits >= 1 && p.splits <= 65535 && p.KV <= 65535 && p.rows <= 65535, "attention_decode: grid too large");
-  DK_REQUIRE(p.splits == 1 || p.scratch != nullptr, "attention_decode: %d splits need a scratch buffer", p.splits);
+  DK_REQUIRE((p.reserved & 2) == 0 || p.splits <= 8, "attention_decode: a cluster merges at most 8 splits, not %d", p.splits);
+  DK_REQUIRE(p.splits == 1 || (p.reserved & 2) != 0 || p.scratch != nullptr, "attention_decode: %d splits need a scratch buffer", p.splits);
   DK_REQUIRE(p.q_stride % 2 == 0, "attention_decode: q stride must be even");
   DK_REQUIRE(p.fuse >= 0 && p.fuse <= 2, "attention_decode: fuse must be 0, 1 or 2");
   DK_REQUIRE(p.fuse == 0 || p.q_stride >= (p.H + 2 * p.KV) * p.hd,
@@ -728,6 +855,7 @@ extern "C" int dk_attention_decode_static(const DkAttnParams* pp, cudaStream_t s
   DK_REQUIRE(pp != nullptr, "attention_decode_static: no parameters");
   DkAttnParams p = *pp;
   p.scratch = nullptr;
+  p.reserved &= ~2;          // the splits go through the built-in scratch here, not through a cluster
   if (p.rows == 0) return 0;
   const long long need = dk_attention_decode_scratch_floats(p.rows, p.H, p.hd, p.splits);
   DK_REQUIRE(need <= (long long)DK_STATIC_SCRATCH_FLOATS,

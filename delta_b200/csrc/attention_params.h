@@ -30,5 +30,7 @@ struct DkAttnParams {
   int fuse;                // decode kernel: q points into rows [q | k | v] that are not rotated yet; the kernel rotates
                            // q and k itself and (fuse == 2) appends k and v of the new token to its page
   int rope_positions;      // rows of rope_table
-  int reserved;            // bit 0 (decode kernel): the pages of the rows lie scattered over the pool, do not look for runs
+  int reserved;            // bit 0 (decode kernel): the pages of the rows lie scattered over the pool, do not look for runs;
+                           // bit 1 (decode kernel, 2..8 splits): the splits of a (row, kv head) are launched as one cluster and
+                           // merge through distributed shared memory (no scratch buffer, no merge kernel)
 };

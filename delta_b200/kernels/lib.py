@@ -50,6 +50,7 @@ _SIGNATURES = {
     "dk_attention_decode": [C.POINTER(AttnParams), P],
     "dk_attention_decode_supported": [I, I, I, I, I],
     "dk_attention_decode_blocks_per_sm": [I, I, I, I],
+    "dk_attention_decode_max_clusters": [I, I, I, I, I],
     "dk_attention_prefill": [C.POINTER(AttnParams), I, P],
     "dk_attention_prefill_supported": [I, I, I, I, I],
     "dk_attention_prefill_tc": [C.POINTER(AttnParams), I, P],

@@ -209,6 +209,17 @@ def attention_decode_blocks_per_sm(H, KV, hd, block_entries) -> int:
     return _decode_occupancy[key]
 
 
+def attention_decode_max_clusters(H, KV, hd, block_entries, splits) -> int:
+    """Clusters of ``splits`` blocks of the decode kernel that the current device holds at once (asked of the runtime once)."""
+    key = (torch.cuda.current_device(), H, KV, hd, block_entries, splits)
+    if key not in _decode_occupancy:
+        n = int(_l.load().dk_attention_decode_max_clusters(H, KV, hd, block_entries, splits))
+        if n < 1:
+            raise KernelError("attention_decode: " + _l.load().dk_last_error().decode("utf-8", "replace"))
+        _decode_occupancy[key] = n
+    return _decode_occupancy[key]
+
+
 def attention_decode_scratch_floats(rows, H, hd, splits) -> int:
     return int(_l.load().dk_attention_decode_scratch_floats(rows, H, hd, splits))
 

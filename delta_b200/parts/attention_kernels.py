@@ -21,6 +21,12 @@ import torch
 from ..kernels import ops
 
 _NO_RUNS = os.environ.get("DELTA_B200_DECODE_NO_TMA") == "1"   # for measurements: never look for runs of pages
+_NO_CLUSTER = os.environ.get("DELTA_B200_DECODE_NO_CLUSTER") == "1"   # for measurements: splits always merged by the second kernel
+# The most splits of a (row, key-value head) that are launched as one thread-block cluster, which merges them itself.
+# Measured on the decode step (Yi-6B shape, context 4,096): 4 splits (batch 16) 3.89 -> 3.78 ms, 2 splits (batch 32)
+# 4.34 -> 4.30 ms, 5 splits (batch 14) 3.76 -> 3.72 ms; 8 splits (batch 8) no gain, and 6 to 8 splits at batches 9 to
+# 12 lose half a millisecond, because fewer of the larger clusters fit on the device at once than blocks do.
+CLUSTER_SPLITS = int(os.environ.get("DELTA_B200_CLUSTER_SPLITS", "5"))
 DECODE_TILE = 64
 MAX_SPLITS = 64
 TMA_MIN_TILES = int(os.environ.get("DELTA_B200_TMA_MIN_TILES", "16"))    # tiles a block must walk for the decode kernel's TMA variant to be taken
@@ -79,14 +85,20 @@ def _decode(ctx, params, row_filter: int, group: str) -> None:
     if held < per_sm:
         per_sm = held
         splits = decode_splits(rows, params.KV, max_keys, ctx.sm_count, per_sm)
+    # A few splits are launched as one cluster that merges them over distributed shared memory: no partial
+    # results in global memory, no second kernel.
+    cluster = 2 <= splits <= CLUSTER_SPLITS and not _NO_CLUSTER
+    if cluster:    # only when all clusters run at once: a second wave would cost more than the merge kernel
+        entries = -(-(-(-params.max_pages // splits)) // tile_pages) * tile_pages
+        cluster = rows * params.KV <= ops.attention_decode_max_clusters(params.H, params.KV, params.hd, entries, splits)
     params.splits = splits
     params.row_filter = row_filter
     # The variant that fetches runs of pages by TMA pays for finding the runs at the start of a block:
     # it wins when a block walks many tiles (batch 64 at 4,096 keys: 111 -> 85 us) and loses a little
     # when it walks few (batch 8 at 4,096 keys with 9 splits, 7 tiles a block: +1.6 % on the step).
     long_blocks = -(-max_keys // (DECODE_TILE * splits)) >= TMA_MIN_TILES
-    params.reserved = 0 if (long_blocks and not _NO_RUNS and not _pages_scattered(ctx, group)) else 1
-    if splits > 1:
+    params.reserved = (0 if (long_blocks and not _NO_RUNS and not _pages_scattered(ctx, group)) else 1) | (2 if cluster else 0)
+    if splits > 1 and not cluster:
         n = ops.attention_decode_scratch_floats(rows, params.H, params.hd, splits)
         bound = _partials_bound(max(ctx.max_rows, rows), params.H, params.KV, params.hd, ctx.cache.max_seq_len, ctx.sm_count, per_sm)
         params.scratch = ctx.scratch(PARTIALS, (n,), torch.float32, bound=(bound,)).data_ptr()

@@ -435,6 +435,61 @@ def test_attention_decode_against_plain(G, KV, hd, ps, pages):
     assert_heads_close(out, refw, H, hd, "window")
 
 
+@pytest.mark.parametrize("pages", ["scattered, told so", "runs"])
+@pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (1, 3, 64, 8), (16, 1, 128, 64), (5, 2, 64, 32)])
+def test_attention_decode_splits_merged_by_a_cluster(G, KV, hd, ps, pages):
+    """Two to eight splits launched as one thread-block cluster, which merges them over distributed shared
+    memory, give the bits of the same splits merged by the second kernel: outputs and log-sum-exp, whole
+    contexts, a window, chosen pages, the score dump; requests shorter than the splits leave blocks empty."""
+    o = ops()
+    H = G * KV
+    seq_lens = [1, ps + 1, 63, 64, 65, 400, 1000, 2500]
+    B = len(seq_lens)
+    case = PagedCase(torch.bfloat16, H, KV, hd, ps, seq_lens, [1] * B, seed=G + hd + 1, scatter=pages != "runs")
+    ref, ref_lse, _ = case.reference()
+    k = 12
+    flags = i32([1] * B)
+    sel_pages = torch.zeros(B, k, dtype=torch.int32, device=DEV)
+    sel_count = torch.full((B,), -1, dtype=torch.int32, device=DEV)
+    for b, n in enumerate(seq_lens):
+        npg = (n + ps - 1) // ps
+        if npg > k:
+            chosen = sorted(random.Random(b).sample(range(npg - 1), k - 1) + [npg - 1])
+            sel_pages[b] = i32(chosen)
+            sel_count[b] = k
+    variants = [dict(), dict(window=ps + 5), dict(row_flags=flags, sel_pages=sel_pages, sel_count=sel_count)]
+    if pages != "runs":
+        variants.append(dict(row_flags=flags, dump=True))
+    for splits in (2, 3, 5, 8):
+        scratch = torch.empty(o.attention_decode_scratch_floats(B, H, hd, splits), device=DEV)
+        for kw in variants:
+            got = {}
+            for cluster in (False, True):
+                kw2 = dict(kw)
+                dump = None
+                if kw2.pop("dump", False):
+                    dump = torch.full((B, H, 2560), float("nan"), device=DEV)
+                    kw2["dump"] = dump
+                out = torch.full((B, H * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+                lse = torch.full((B, H), 9.0, device=DEV)
+                p = case.params(out, lse=lse, scratch=None if cluster else scratch, splits=splits, **kw2)
+                p.reserved = (1 if pages != "runs" else 0) | (2 if cluster else 0)
+                o.attention_decode(p)
+                got[cluster] = (out, lse, dump)
+            what = f"splits={splits}, {sorted(kw)}"
+            assert torch.equal(got[True][0], got[False][0]), what
+            assert torch.equal(got[True][1], got[False][1]), what + ": log-sum-exp"
+            if got[True][2] is not None:
+                assert torch.equal(torch.nan_to_num(got[True][2], nan=-7.0), torch.nan_to_num(got[False][2], nan=-7.0)), what + ": dump"
+            if not kw:
+                assert_heads_close(got[True][0], ref, H, hd, what)
+                assert torch.allclose(got[True][1].cpu(), ref_lse, atol=1e-3, rtol=1e-5)
+    with pytest.raises(o.KernelError, match="at most 8 splits"):
+        p = case.params(torch.empty((B, H * hd), dtype=torch.bfloat16, device=DEV), splits=9)
+        p.reserved = 2
+        o.attention_decode(p)
+
+
 @pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05", "tcgen05_runs"])
 @pytest.mark.parametrize("H, KV, hd, ps", [(8, 2, 128, 16), (3, 3, 64, 8), (4, 1, 64, 64), (32, 4, 128, 32)])
 def test_attention_prefill_against_plain(H, KV, hd, ps, kernel):
