@@ -43,8 +43,11 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 // WARPS: warps of a block that split K between them.  Fewer warps make blocks small enough that
 // all of them are resident at once (no second, partly filled wave); more warps shorten the
 // chain of memory round trips of a block when there are few blocks anyway.
-template <int NT, int SETS, typename TO, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
+// MINB: blocks per SM asked of the compiler.  With 8 rows (NT = 1) the kernel takes 70 registers, three blocks
+// of 256 threads per SM; held to 64 it takes four, which is worth it only where it saves a wave (7,168 weight
+// rows are 448 blocks: four blocks too many for three per SM on 148 SMs) and costs a little elsewhere.
+template <int NT, int SETS, typename TO, int WARPS, int MINB = 0>
+__global__ void __launch_bounds__(WARPS * 32, MINB) gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                                                                TO* __restrict__ out, int M, int N, int K, int lda, int ldw,
                                                                int ldc, int set_stride_rows) {
   constexpr int THREADS = WARPS * 32;
@@ -151,8 +154,24 @@ void launch(const void* x, const void* W, void* out, int M, int N, int K, int ld
 #define GO_W(W_)                                                                                                  \
   gemm_small_m_kernel<NT, SETS, TO, W_><<<tiles, W_ * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, \
                                                                         (TO*)out, M, N, K, lda, ldw, ldc, set_stride)
-  if (SETS == 2) GO_W(4);
-  else GO_W(8);
+  if constexpr (SETS == 2) {
+    GO_W(4);
+  } else if constexpr (NT == 1) {
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int waves3 = (tiles + 3 * sms - 1) / (3 * sms), waves4 = (tiles + 4 * sms - 1) / (4 * sms);
+    if (waves4 < waves3)
+      gemm_small_m_kernel<NT, SETS, TO, 8, 4><<<tiles, 8 * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TO*)out, M, N, K,
+                                                                          lda, ldw, ldc, set_stride);
+    else
+      GO_W(8);
+  } else {
+    GO_W(8);
+  }
 #undef GO_W
 }
 }  // namespace

@@ -27,7 +27,19 @@ _BUCKETS = (8, 16, 32, 64, 128)
 _choice: Dict[tuple, str] = {}
 _times: Dict[tuple, Dict[str, float]] = {}
 _flush: Optional[torch.Tensor] = None
-MARGIN = 0.08         # another kernel replaces the preferred one only when it is this much faster
+# Another kernel replaces the preferred one only when it is faster by more than ``margin(t)`` microseconds: a
+# product of another kind than its neighbours costs 2 to 3 us more in the step than alone, and below 3 % two
+# measurements of the same kernel differ.  (A margin of 8 % of the time, as it was, kept the small-batch kernel
+# for the 50 to 140 us products of the Yi-34B shape where the library is 6 to 9 us faster, in some runs and
+# not in others: 14.4 against 13.2 ms a step.)
+MARGIN_US = 2.5
+MARGIN_REL = 0.03
+
+
+def margin(t_us: float) -> float:
+    return max(MARGIN_US, MARGIN_REL * t_us)
+
+
 TUNE = os.environ.get("DELTA_B200_NO_TUNE") != "1"   # off: the first candidate of a shape is taken unmeasured
 
 
@@ -92,7 +104,7 @@ def _time(fn, reps: int = 12) -> float:
 def _tune(m: int, x, w, swiglu: bool, out_dtype, err) -> str:
     """Times every candidate on these weights with ``m`` rows.  The first candidate (the order of
     ``_candidates`` is the order of preference) stays unless another is faster by more than
-    ``MARGIN``: differences below that are within the noise of a measurement in isolation, and a
+    ``margin``: differences below that are within the noise of a measurement in isolation, and a
     choice that changes from run to run costs more in the step than it gains here."""
     global _flush
     n, k = w.shape
@@ -113,7 +125,7 @@ def _tune(m: int, x, w, swiglu: bool, out_dtype, err) -> str:
         except (ops.KernelError, RuntimeError):
             continue
         _times.setdefault((m, n, k, swiglu), {})[kind] = t
-        if t < best_t * (1.0 if best_t == float("inf") else 1.0 - MARGIN):
+        if best_t == float("inf") or t < best_t - margin(best_t):
             best, best_t = kind, t
     torch.cuda.synchronize()
     return best

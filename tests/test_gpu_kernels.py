@@ -165,7 +165,7 @@ def test_gemm_plain_float32_is_true_32_bit(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 17, 33, 64])
-@pytest.mark.parametrize("N, K", [(96, 40), (1056, 344), (4096, 4096)])
+@pytest.mark.parametrize("N, K", [(96, 40), (1056, 344), (4096, 4096), (7168, 264)])   # 7,168 rows: the variant held to four blocks per SM
 def test_gemm_small_m(M, N, K):
     o = ops()
     x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
@@ -801,11 +801,14 @@ def test_product_tuner_keeps_the_preferred_kernel_within_the_margin(monkeypatch)
         return linear._tune(M, x, w, False, torch.bfloat16, err)
 
     n = len(cands)
-    assert tuned([10.0] * n) == cands[0]
-    assert tuned([10.0] + [10.0 * (1 - linear.MARGIN) + 0.01] * (n - 1)) == cands[0]      # not enough
-    assert tuned([10.0, 9.0] + [10.0] * (n - 2)) == cands[1]                               # 10 % faster
-    assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.5]) == cands[1]                       # 5.6 % on the second: stays
-    assert tuned([10.0, 9.0] + [10.0] * (n - 3) + [8.0]) == cands[-1]
+    assert linear.margin(20.0) == 2.5 and linear.margin(200.0) == 6.0
+    assert tuned([20.0] * n) == cands[0]
+    assert tuned([20.0] + [17.6] * (n - 1)) == cands[0]                                    # 2.4 us faster: not enough
+    assert tuned([20.0, 17.0] + [20.0] * (n - 2)) == cands[1]                              # 3 us faster
+    assert tuned([20.0, 17.0] + [20.0] * (n - 3) + [15.0]) == cands[1]                     # 2 us on the second: stays
+    assert tuned([20.0, 17.0] + [20.0] * (n - 3) + [14.0]) == cands[-1]
+    assert tuned([200.0, 195.0] + [200.0] * (n - 2)) == cands[0]                           # 2.5 % of a long product: noise
+    assert tuned([200.0, 193.0] + [200.0] * (n - 2)) == cands[1]
 
 
 def test_decode_attention_splits_follow_the_occupancy_at_long_contexts():
