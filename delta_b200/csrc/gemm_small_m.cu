@@ -14,6 +14,7 @@
 // rows that belong to its 16 "gate" rows and writes silu(gate) * up (reference
 // model.py:514).
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -46,12 +47,14 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 // MINB: blocks per SM asked of the compiler.  With 8 rows (NT = 1) the kernel takes 70 registers, three blocks
 // of 256 threads per SM; held to 64 it takes four, which is worth it only where it saves a wave (7,168 weight
 // rows are 448 blocks: four blocks too many for three per SM on 148 SMs) and costs a little elsewhere.
-template <int NT, int SETS, typename TO, int WARPS, int MINB = 0>
+// DEEP: twice as many chunks in flight per thread (half as many round trips to memory per block), at 2 blocks per SM:
+// for products of so few blocks that no more than two fall to an SM anyway.
+template <int NT, int SETS, typename TO, int WARPS, int MINB = 0, bool DEEP = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB) gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                                                                TO* __restrict__ out, int M, int N, int K, int lda, int ldw,
                                                                int ldc, int set_stride_rows) {
   constexpr int THREADS = WARPS * 32;
-  constexpr int U = NT <= 2 ? 4 : 2;  // chunks in flight per thread
+  constexpr int U = (NT <= 2 ? 4 : 2) * (DEEP ? 2 : 1);  // chunks in flight per thread
   __shared__ float red[WARPS][16][8 * NT + 1];
   const int n0 = blockIdx.x * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -164,7 +167,13 @@ void launch(const void* x, const void* W, void* out, int M, int N, int K, int ld
       if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const int waves3 = (tiles + 3 * sms - 1) / (3 * sms), waves4 = (tiles + 4 * sms - 1) / (4 * sms);
-    if (waves4 < waves3)
+    // (measured in the decode step of the Yi-6B shape, batch 8: 3.265 -> 3.227 ms with the deep instance for the
+    // products of 256 blocks; held to three blocks per SM the compiler no longer keeps the loads in flight and nothing is gained)
+    static const bool deep_off = getenv("DELTA_B200_SMALL_M_NO_DEEP") != nullptr;
+    if (!deep_off && tiles <= 2 * sms)
+      gemm_small_m_kernel<NT, SETS, TO, 8, 2, true><<<tiles, 8 * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TO*)out, M, N,
+                                                                                K, lda, ldw, ldc, set_stride);
+    else if (waves4 < waves3)
       gemm_small_m_kernel<NT, SETS, TO, 8, 4><<<tiles, 8 * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TO*)out, M, N, K,
                                                                           lda, ldw, ldc, set_stride);
     else
