@@ -74,6 +74,52 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) gemm_small_m_kernel(const __
   }
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+  if constexpr (DEEP) {
+    // Two halves of the chunks in flight take turns: while one is multiplied the other is on its way, so the
+    // requests of a block never run dry between rounds (a round of this kernel is as long as the memory
+    // needs for its bytes, and the pause between rounds was a fifth of the time of a long product).
+    constexpr int H = U / 2;
+    uint4 wa[H][SETS][2], wb[H][SETS][2], xa[H][NT], xb[H][NT];
+    auto fetch = [&](uint4 (&wv)[H][SETS][2], uint4 (&xv)[H][NT], int c0) {
+#pragma unroll
+      for (int u = 0; u < H; ++u) {
+        const int c = c0 + u * WARPS;
+        const int k = c * 32 + t * 8;
+        const bool ok = c < n_chunks && k < K;
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+          wv[u][s][0] = ok ? ld_stream(wrow[s][0] + k) : zero;
+          wv[u][s][1] = ok ? ld_stream(wrow[s][1] + k) : zero;
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const int m = j * 8 + g;
+          xv[u][j] = (ok && m < M) ? ld_keep(x + (size_t)m * lda + k) : zero;
+        }
+      }
+    };
+    auto multiply = [&](const uint4 (&wv)[H][SETS][2], const uint4 (&xv)[H][NT]) {
+#pragma unroll
+      for (int u = 0; u < H; ++u) {
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+          const uint4 a = wv[u][s][0], b = wv[u][s][1];
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            mma_bf16(acc[s][j], a.x, b.x, a.y, b.y, xv[u][j].x, xv[u][j].y);
+            mma_bf16(acc[s][j], a.z, b.z, a.w, b.w, xv[u][j].z, xv[u][j].w);
+          }
+        }
+      }
+    };
+    fetch(wa, xa, warp);
+    for (int c0 = warp; c0 < n_chunks; c0 += 2 * H * WARPS) {
+      fetch(wb, xb, c0 + H * WARPS);
+      multiply(wa, xa);
+      fetch(wa, xa, c0 + 2 * H * WARPS);
+      multiply(wb, xb);
+    }
+  } else
   for (int c0 = warp; c0 < n_chunks; c0 += WARPS * U) {
     uint4 wv[U][SETS][2];
     uint4 xv[U][NT];
