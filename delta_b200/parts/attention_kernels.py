@@ -28,7 +28,7 @@ _NO_CLUSTER = os.environ.get("DELTA_B200_DECODE_NO_CLUSTER") == "1"   # for meas
 # 12 lose half a millisecond, because fewer of the larger clusters fit on the device at once than blocks do.
 CLUSTER_SPLITS = int(os.environ.get("DELTA_B200_CLUSTER_SPLITS", "5"))
 DECODE_TILE = 64
-MAX_SPLITS = 64
+MAX_SPLITS = int(os.environ.get("DELTA_B200_MAX_SPLITS", "64"))
 TMA_MIN_TILES = int(os.environ.get("DELTA_B200_TMA_MIN_TILES", "16"))    # tiles a block must walk for the decode kernel's TMA variant to be taken
 TC_PREFILL_MIN_TOKENS = 32   # below this a 128-query tile of the tcgen05 kernel is mostly padding
 PARTIALS = "attention.decode_partials"
@@ -36,10 +36,12 @@ PARTIALS = "attention.decode_partials"
 
 def decode_splits(rows: int, kv_heads: int, max_keys: int, sm_count: int, blocks_per_sm: int) -> int:
     """Blocks per (row, key-value head): as many as run at once (a second, partly filled
-    wave would double the time), no more than there are 64-key tiles."""
+    wave would double the time), and so few that a block has two 64-key tiles at the longest context (one
+    request at 4,096 keys: 64 blocks of one tile each 2.914 ms a step, 32 blocks of two 2.877 ms; at
+    32,768 keys 64 blocks of eight tiles beat 32 of sixteen, 3.276 against 3.345 ms)."""
     want = (max(1, blocks_per_sm) * sm_count) // max(1, rows * kv_heads)
     tiles = max(1, -(-max_keys // DECODE_TILE))
-    return max(1, min(want, tiles, MAX_SPLITS))
+    return max(1, min(want, max(1, tiles // 2), MAX_SPLITS))
 
 
 @functools.lru_cache(maxsize=None)

@@ -120,7 +120,9 @@ def test_scratch_addresses_stay_when_graphs_of_other_sizes_are_recorded(folders)
     from delta_b200.config.selective_cache import SelectiveCacheConfig
     from delta_b200.engine.step import ModelRunner, RowInput
     sel = SelectiveCacheConfig(full_cache_layers=(0,), subset_cache_size=3, L=2)
-    cfg = EngineConfig(max_batch=8, max_seq_len=512, page_size=PS, dtype="bfloat16", cuda_graph_decode=True,
+    # (2,048 tokens at most: then a request is split more than five ways, which go through the buffer of partial
+    # results and the merge kernel; up to five splits merge inside a cluster and need no buffer)
+    cfg = EngineConfig(max_batch=8, max_seq_len=2048, page_size=PS, dtype="bfloat16", cuda_graph_decode=True,
                        options=dict(selective_cache=sel))
     r = ModelRunner(folders["hd128g3"], engine_config=cfg)
     vocab = ODD["hd128g3"]["vocab_size"]
