@@ -9,6 +9,9 @@ import torch
 from ..cache.manager import CacheManager, LayerCacheView
 
 
+_SM_COUNT = {}     # device -> number of SMs (asked once)
+
+
 class StepContext:
     """One batch of (request, its next tokens).
 
@@ -64,6 +67,14 @@ class StepContext:
         self.capture = capture
         self._scratch_pool = scratch_pool
         self._once = set()
+        self._memo = {}
+
+    def memo(self, key, make):
+        """``make()`` the first time it is asked with this key in a step, its value from then on: for what every
+        layer of a step would otherwise work out again from the same rows."""
+        if key not in self._memo:
+            self._memo[key] = make()
+        return self._memo[key]
 
     def once(self, key: str) -> bool:
         """True the first time it is asked with this key in a step."""
@@ -84,11 +95,14 @@ class StepContext:
     def any_row_flag(self, bit: int) -> bool:
         """True when some row of the step has this flag set; in a replayable step always
         (the rows of a later replay may have it, the kernels look at ``row_flags``)."""
-        return self.replayable or any(r.flags & bit for r in self.host["rows"])
+        return self.replayable or self.memo(("row flag", bit), lambda: any(r.flags & bit for r in self.host["rows"]))
 
     @property
     def sm_count(self) -> int:
-        return torch.cuda.get_device_properties(self.device).multi_processor_count
+        n = _SM_COUNT.get(self.device)
+        if n is None:
+            n = _SM_COUNT[self.device] = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return n
 
     def scratch(self, key: str, shape, dtype, bound=None) -> torch.Tensor:
         """Working memory that lives across steps.  ``bound`` is the largest shape the part

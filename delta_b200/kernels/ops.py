@@ -44,6 +44,10 @@ def _stream():
     return _raw_stream(_current_device())
 
 
+def _device_index() -> int:
+    return _current_device() if _current_device is not None else torch.cuda.current_device()
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _current_device = getattr(torch._C, "_cuda_getDevice", None)
 if _raw_stream is None or _current_device is None:      # a torch without these entry points: the public, slower way
@@ -150,18 +154,12 @@ def gemm_nt_plain(a, w, out):
     return out
 
 
-def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, KV, hd, ps, scale, row_slot=None,
-                     row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None, sel_pages=None,
-                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0, row_filter=0,
-                     fuse=0, rope_table=None) -> AttnParams:
+def attn_step_params(*, tok_row, tok_pos, row_slot=None, row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None,
+                     err=None) -> AttnParams:
+    """The part of the attention kernels' parameters that is the same for every layer of a step (the step's
+    tokens and rows): made once per step and handed to ``make_attn_params`` as ``step``."""
     p = AttnParams()
     i32 = torch.int32
-    p.q = _ptr(q, "q")
-    p.out = _ptr(out, "out", q.dtype)
-    p.kv = _ptr(kv, "kv", q.dtype)
-    if tuple(kv.shape[1:]) != (2, KV, ps, hd):
-        raise KernelError(f"attention: cache has shape {tuple(kv.shape)}, expected [pages, 2, {KV}, {ps}, {hd}]")
-    p.block_table = _ptr(block_table, "block_table", i32)
     p.tok_row = _ptr(tok_row, "tok_row", i32)
     p.tok_pos = _ptr(tok_pos, "tok_pos", i32)
     p.row_slot = _ptr(row_slot, "row_slot", i32)
@@ -169,13 +167,40 @@ def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row, tok_pos, H, 
     p.row_q_start = _ptr(row_q_start, "row_q_start", i32)
     p.row_q_len = _ptr(row_q_len, "row_q_len", i32)
     p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
+    p.err = _ptr(err, "err", i32)
+    p.T = tok_row.shape[0]
+    return p
+
+
+def make_attn_params(*, q, q_stride, out, kv, block_table, tok_row=None, tok_pos=None, H, KV, hd, ps, scale, row_slot=None,
+                     row_flags=None, row_q_start=None, row_q_len=None, row_pos_start=None, sel_pages=None,
+                     sel_count=None, dump=None, lse=None, scratch=None, err=None, window=0, splits=0, row_filter=0,
+                     fuse=0, rope_table=None, step: Optional[AttnParams] = None) -> AttnParams:
+    i32 = torch.int32
+    if step is not None:
+        p = AttnParams.from_buffer_copy(step)
+    else:
+        p = AttnParams()
+        p.tok_row = _ptr(tok_row, "tok_row", i32)
+        p.tok_pos = _ptr(tok_pos, "tok_pos", i32)
+        p.row_slot = _ptr(row_slot, "row_slot", i32)
+        p.row_flags = _ptr(row_flags, "row_flags", i32)
+        p.row_q_start = _ptr(row_q_start, "row_q_start", i32)
+        p.row_q_len = _ptr(row_q_len, "row_q_len", i32)
+        p.row_pos_start = _ptr(row_pos_start, "row_pos_start", i32)
+        p.err = _ptr(err, "err", i32)
+        p.T = tok_row.shape[0]
+    p.q = _ptr(q, "q")
+    p.out = _ptr(out, "out", q.dtype)
+    p.kv = _ptr(kv, "kv", q.dtype)
+    if tuple(kv.shape[1:]) != (2, KV, ps, hd):
+        raise KernelError(f"attention: cache has shape {tuple(kv.shape)}, expected [pages, 2, {KV}, {ps}, {hd}]")
+    p.block_table = _ptr(block_table, "block_table", i32)
     p.sel_pages = _ptr(sel_pages, "sel_pages", i32)
     p.sel_count = _ptr(sel_count, "sel_count", i32)
     p.dump = _ptr(dump, "dump", torch.float32)
     p.lse = _ptr(lse, "lse", torch.float32)
     p.scratch = _ptr(scratch, "scratch")
-    p.err = _ptr(err, "err", i32)
-    p.T = tok_row.shape[0]
     p.rows = block_table.shape[0]
     p.H, p.KV, p.hd, p.ps = H, KV, hd, ps
     p.max_pages = block_table.shape[1]
@@ -209,7 +234,7 @@ _decode_occupancy = {}
 
 def attention_decode_blocks_per_sm(H, KV, hd, block_entries) -> int:
     """Blocks of the decode kernel one SM of the current device holds at once (asked of the runtime once)."""
-    key = (torch.cuda.current_device(), H, KV, hd, block_entries)
+    key = (_device_index(), H, KV, hd, block_entries)
     if key not in _decode_occupancy:
         n = int(_l.load().dk_attention_decode_blocks_per_sm(H, KV, hd, block_entries))
         if n < 1:
@@ -220,7 +245,7 @@ def attention_decode_blocks_per_sm(H, KV, hd, block_entries) -> int:
 
 def attention_decode_max_clusters(H, KV, hd, block_entries, splits) -> int:
     """Clusters of ``splits`` blocks of the decode kernel that the current device holds at once (asked of the runtime once)."""
-    key = (torch.cuda.current_device(), H, KV, hd, block_entries, splits)
+    key = (_device_index(), H, KV, hd, block_entries, splits)
     if key not in _decode_occupancy:
         n = int(_l.load().dk_attention_decode_max_clusters(H, KV, hd, block_entries, splits))
         if n < 1:

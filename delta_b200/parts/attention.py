@@ -118,13 +118,15 @@ class GQAAttention(Mixer):
             dump = ctx.scratch("delta.dump", (ctx.num_rows, H, ctx.max_pages * cache.page_size), torch.float32,
                                bound=(ctx.max_rows, H, widest * cache.page_size))
             lse = ctx.scratch("delta.lse", (T, H), torch.float32, bound=(ctx.max_step_tokens, H))
+        step = ctx.memo("attention.step_params", lambda: ops.attn_step_params(
+            tok_row=ctx.tok_row, tok_pos=ctx.tok_pos, row_slot=ctx.row_slot, row_flags=ctx.row_flags, row_q_start=ctx.row_q_start,
+            row_q_len=ctx.row_q_len, row_pos_start=ctx.row_pos_start, err=ctx.err))
         params = ops.make_attn_params(
-            q=qkv, q_stride=qkv.shape[1], out=out, kv=cache.pages, block_table=cache.block_table, tok_row=ctx.tok_row,
-            tok_pos=ctx.tok_pos, H=H, KV=KV, hd=hd, ps=cache.page_size, scale=self.scale, row_slot=ctx.row_slot,
-            row_flags=ctx.row_flags, row_q_start=ctx.row_q_start, row_q_len=ctx.row_q_len, row_pos_start=ctx.row_pos_start,
+            step=step, q=qkv, q_stride=qkv.shape[1], out=out, kv=cache.pages, block_table=cache.block_table,
+            H=H, KV=KV, hd=hd, ps=cache.page_size, scale=self.scale,
             sel_pages=ctx.state(SELECTED_PAGES) if (self.role == "subset" and selective) else None,
             sel_count=ctx.state(SELECTED_COUNT) if (self.role == "subset" and selective) else None,
-            dump=dump, lse=lse, err=ctx.err, window=self.window or 0,
+            dump=dump, lse=lse, window=self.window or 0,
             fuse=(2 if cache.writes else 1) if fuse else 0, rope_table=table if fuse else None)
         attention_kernels.run(ctx, params, cache.group)
         if self.role == "planner" and selective:

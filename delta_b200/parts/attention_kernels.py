@@ -68,10 +68,13 @@ def _pages_scattered(ctx, group: str) -> bool:
     g = ctx.cache.groups[group]
     if ctx.replayable:
         return g.pool.shuffled
-    t = g.table[[r.slot for r in ctx.host["rows"]]]
-    held = t[:, 1:] >= 0
-    n = int(held.sum())
-    return n > 0 and int(((t[:, 1:] - t[:, :-1] == 1) & held).sum()) * 2 < n
+
+    def look():
+        t = g.table[[r.slot for r in ctx.host["rows"]]]
+        held = t[:, 1:] >= 0
+        n = int(held.sum())
+        return n > 0 and int(((t[:, 1:] - t[:, :-1] == 1) & held).sum()) * 2 < n
+    return ctx.memo(("pages scattered", group), look)     # the same for every layer of the group in this step
 
 
 def _decode(ctx, params, row_filter: int, group: str) -> None:
