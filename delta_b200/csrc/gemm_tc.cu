@@ -244,8 +244,12 @@ extern "C" int dk_gemm_tc_supported(int M, int N, int K, int swiglu) {
 }
 
 // splits: blocks that share K as one cluster (1, 2, 4 or 8).  out_dtype DK_BF16 or DK_F32.
+// per_sm: 1, or 2 to size the ring of stages so that two blocks share an SM's shared memory (stages of half the
+// length): with more tiles than SMs but no more than twice as many (11,008 SwiGLU columns are 172 tiles), all
+// blocks then run at once instead of a full wave and a short one.
 extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int lda, int ldw, int ldc,
-                          int out_dtype, int swiglu, int splits, int* err, cudaStream_t stream) {
+                          int out_dtype, int swiglu, int splits, int per_sm, int* err, cudaStream_t stream) {
+  DK_REQUIRE(per_sm == 1 || per_sm == 2, "gemm_tc: per_sm must be 1 or 2, got %d", per_sm);
   DK_REQUIRE(dk_gemm_tc_supported(M, N, K, swiglu), "gemm_tc: sizes not taken: M=%d N=%d K=%d swiglu=%d", M, N, K, swiglu);
   DK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: splits must be 1, 2, 4 or 8, got %d", splits);
   DK_REQUIRE((lda % 8) == 0 && (ldw % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0,
@@ -264,10 +268,10 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   a.tmem_cols = a.mpad <= 32 ? 32 : (a.mpad <= 64 ? 64 : 128);
   const int a_bytes = TILE_ROWS * KSTEP * 2;
   const int b_bytes = a.mpad * KSTEP * 2;
-  a.ksub = a.mpad <= 64 ? KSUB_MAX : 2;
+  a.ksub = per_sm == 2 ? 2 : (a.mpad <= 64 ? KSUB_MAX : 2);
   const int stage_bytes = a.ksub * (a_bytes + b_bytes);
   const int part_bytes = a.mpad * TILE_ROWS * 4;
-  int stages = (224 * 1024 - 1024) / stage_bytes;
+  int stages = ((224 * 1024) / per_sm - 2048) / stage_bytes;
   if (stages > 8) stages = 8;
   DK_REQUIRE(stages >= 2, "gemm_tc: M=%d leaves no room for two stages", M);
   a.stages = stages;

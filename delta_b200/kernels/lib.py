@@ -57,7 +57,7 @@ _SIGNATURES = {
     "dk_attention_prefill_tc_supported": [I, I, I, I, I, I],
     "dk_gemm_small_m": [P, P, P, I, I, I, I, I, I, I, I, P],
     "dk_gemm_small_m_supported": [I, I, I, I],
-    "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+    "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "dk_gemm_tc_supported": [I, I, I, I],
     "dk_gemm_stream_k_supported": [I, I, I, I],
     "dk_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, I, P, P, P],

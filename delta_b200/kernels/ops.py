@@ -309,17 +309,18 @@ def gemm_tc_supported(M, N, K, swiglu=False) -> bool:
     return bool(_l.load().dk_gemm_tc_supported(M, N, K, int(swiglu)))
 
 
-def gemm_tc(x, w, out, swiglu=False, splits=1, err=None):
+def gemm_tc(x, w, out, swiglu=False, splits=1, err=None, per_sm=1):
     """out = x @ w^T for up to 128 rows of bfloat16 x on the tcgen05 tensor cores; the weights
     stream through shared memory by TMA.  ``splits`` blocks (1, 2, 4, 8) share K as a cluster.
-    ``swiglu``: w holds gate rows then up rows, out [M, N/2] = silu(x gate^T) * (x up^T)."""
+    ``swiglu``: w holds gate rows then up rows, out [M, N/2] = silu(x gate^T) * (x up^T).
+    ``per_sm`` 2: shorter stages, so that two blocks fit on an SM."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if swiglu else N
     if w.shape[1] != K or tuple(out.shape) != (M, n_out) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} or dtypes do not fit")
     _l.check(_l.load().dk_gemm_tc(_ptr(x, "x"), _ptr(w, "w"), _ptr(out, "out"), M, N, K, x.stride(0), w.stride(0),
-                                  out.stride(0), dtype_code(out.dtype), int(swiglu), int(splits),
+                                  out.stride(0), dtype_code(out.dtype), int(swiglu), int(splits), int(per_sm),
                                   _ptr(err, "err", torch.int32), _stream()), "gemm_tc")
     return out
 

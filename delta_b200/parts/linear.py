@@ -58,6 +58,10 @@ def _candidates(m: int, n: int, k: int, swiglu: bool, out_dtype) -> List[str]:
         for s in (1, 2, 4, 8):
             if s == 1 or k // (256 * s) >= 2:
                 c.append(f"tc{s}")
+        if m <= 64:
+            c.append("tc1d")     # two blocks per SM (shorter stages): for more tiles than SMs, up to twice as many
+            if k // 512 >= 2:
+                c.append("tc2d")
     if out_dtype == torch.bfloat16:
         c.append("lib")
     if ops.gemm_stream_k_supported(m, n, k, swiglu):
@@ -71,7 +75,8 @@ def _run(kind: str, x, w, out, swiglu: bool, err=None):
     if kind == "sk":
         return ops.gemm_stream_k(x, w, out, swiglu=swiglu, err=err)
     if kind.startswith("tc"):
-        return ops.gemm_tc(x, w, out, swiglu=swiglu, splits=int(kind[2:]), err=err)
+        two = kind.endswith("d")
+        return ops.gemm_tc(x, w, out, swiglu=swiglu, splits=int(kind[2:3]), err=err, per_sm=2 if two else 1)
     ops.count_launch()
     if swiglu:
         gu = torch.mm(x, w.t())
@@ -167,7 +172,7 @@ def load_choices(path) -> int:
     import json
     with open(path) as f:
         items = json.load(f)["product_kernels"]
-    known = {"small", "lib", "sk", "none", "tc1", "tc2", "tc4", "tc8"}
+    known = {"small", "lib", "sk", "none", "tc1", "tc2", "tc4", "tc8", "tc1d", "tc2d"}
     for it in items:
         if it["kernel"] not in known:
             raise ValueError(f"{path}: unknown product kernel '{it['kernel']}'")

@@ -208,6 +208,12 @@ def test_gemm_tc(M, N, K, splits):
     # by at most about K * 2^-24 * 0.1, which is 7e-5 for the longest K here
     other = torch.empty_like(out32)
     o.gemm_tc(x, w, other, splits=1, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(other.float(), ref, atol=2e-2, rtol=1e-2)
+    if M <= 64:         # shorter stages, two blocks to an SM
+        other.fill_(9.0)
+        o.gemm_tc(x, w, other, splits=min(splits, 2), err=err, per_sm=2)
+        o.raise_if_error(err)
     assert torch.allclose(other, out32, atol=5e-4, rtol=1e-5)
 
 
@@ -222,7 +228,7 @@ def test_gemm_tc_swiglu(M, I, K, splits):
     ref = x.float() @ w.float().T
     want = torch.nn.functional.silu(ref[:, :I]) * ref[:, I:]
     act = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
-    o.gemm_tc(x, w, act, swiglu=True, splits=splits, err=err)
+    o.gemm_tc(x, w, act, swiglu=True, splits=splits, err=err, per_sm=2 if M == 64 else 1)
     o.raise_if_error(err)
     assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
 
