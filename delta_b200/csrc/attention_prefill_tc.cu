@@ -177,9 +177,11 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 
   // The four warps that fetch and issue need few registers, the eight softmax warps hold a row of 128 scores each:
   // the first warpgroup gives registers back and the other two take them (384 threads x 168 = 128 x 64 + 256 x 216).
+  // (Each change of the register count stands inside the branch whose code it is for: after a common point the
+  // compiler would have to assume the smaller count for everybody.)
   if (warp >= PRODUCER_WARP0) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
-  if (warp < MMA_WARP) {
+  if (warp < MMA_WARP) {      // (the three branches of this warpgroup keep their indentation)
     // ----------------------------------------------------------- producers
     // one warp for K and one for V, so that the next K is never held up behind a V whose buffer
     // is still being read
