@@ -85,11 +85,11 @@ struct Piece {
   bool valid;
 };
 
-__device__ __forceinline__ Piece piece_of(const DkAttnParams& p, int index, int n_qt) {
+__device__ __forceinline__ Piece piece_of(const DkAttnParams& p, int index, int row_lo, int n_rows) {
   Piece w;
   w.h = index % p.H;
-  w.row = (index / p.H) % p.rows;
-  const int yy = index / (p.H * p.rows);                // 0: the row's latest query tile, which has the most keys
+  w.row = row_lo + (index / p.H) % n_rows;
+  const int yy = index / (p.H * n_rows);                // 0: the row's latest query tile, which has the most keys
   const int q_len = p.row_q_len[w.row];
   w.qt = (q_len + QT - 1) / QT - 1 - yy;
   const int q0 = w.qt * QT;
@@ -119,14 +119,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   using L = Layout<HD>;
   constexpr int STAGES = L::STAGES;
   static_assert(STAGES == 2, "a stage belongs to the tiles of one parity");
-  const int n_pieces = p.H * n_qt * p.rows;
-  // The pieces a block takes: in rounds of gridDim.x pieces, forwards in the even rounds and backwards in the odd ones.
-  // Pieces are numbered from long to short, so a block that got a long one in one round gets a short one in the next,
-  // and all blocks end at about the same time without asking each other anything.
-  auto piece_index = [&](int round) {
-    const int b = (round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
-    return round * (int)gridDim.x + b;
-  };
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -137,6 +129,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   auto row_stat = [&](int w) { return reinterpret_cast<float2*>(smem + L::OFF_P + w * L::P_BYTES); };
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int failed;
+  __shared__ int row_range[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ps = p.ps, G = p.H / p.KV;
@@ -162,12 +155,43 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  // the first piece's row is looked up while the barriers and the tensor memory are set up
-  const Piece first_piece = piece_of(p, (int)blockIdx.x < n_pieces ? (int)blockIdx.x : 0, n_qt);
+  if (warp == 0) {
+    // In a step that also holds single tokens (which the decode kernel takes) only the rows from the first to the
+    // last one that brings several tokens are cut into pieces: a block does not have to walk over hundreds of rows
+    // that are not its business.
+    int lo = p.rows, hi = -1;
+    if (p.row_filter == 2) {
+      for (int r0 = 0; r0 < p.rows; r0 += 32) {
+        const int r = r0 + lane;
+        if (r < p.rows && p.row_q_len[r] > 1) {
+          lo = min(lo, r);
+          hi = max(hi, r);
+        }
+      }
+      lo = __reduce_min_sync(0xffffffffu, lo);
+      hi = __reduce_max_sync(0xffffffffu, hi);
+    } else {
+      lo = 0;
+      hi = p.rows - 1;
+    }
+    if (lane == 0) {
+      row_range[0] = lo;
+      row_range[1] = hi;
+    }
+  }
   if (warp == MMA_WARP) tmem_alloc(s2u(&tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  const int row_lo = row_range[0], n_rows = max(0, row_range[1] - row_range[0] + 1);
+  const int n_pieces = p.H * n_qt * n_rows;
+  // The pieces a block takes: in rounds of gridDim.x pieces, forwards in the even rounds and backwards in the odd ones.
+  // Pieces are numbered from long to short, so a block that got a long one in one round gets a short one in the next,
+  // and all blocks end at about the same time without asking each other anything.
+  auto piece_index = [&](int round) {
+    const int b = (round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    return round * (int)gridDim.x + b;
+  };
   const uint32_t tmem = tmem_slot;
   const uint32_t sm_q = s2u(smem + L::OFF_Q), sm_k = s2u(smem + L::OFF_K), sm_v = s2u(smem + L::OFF_V),
                  sm_p = s2u(smem + L::OFF_P);
@@ -195,7 +219,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     for (int round = 0; round * (int)gridDim.x < n_pieces && !failed; ++round) {
       const int index = piece_index(round);
       if (index >= n_pieces) continue;
-      const Piece w = round == 0 ? first_piece : piece_of(p, index, n_qt);
+      const Piece w = piece_of(p, index, row_lo, n_rows);
       if (!w.valid) continue;
       const int kvh = w.h / G;
       if (kind == 0) {
@@ -268,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     for (int round = 0; ok && round * (int)gridDim.x < n_pieces; ++round) {
       const int index = piece_index(round);
       if (index >= n_pieces) continue;
-      const Piece w = round == 0 ? first_piece : piece_of(p, index, n_qt);
+      const Piece w = piece_of(p, index, row_lo, n_rows);
       if (!w.valid) continue;
       ok = wait_all(q_full, n_done & 1);
       for (int j = 0; ok && j < w.n_tiles; ++j) {
@@ -303,7 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     for (int round = 0; ok && round * (int)gridDim.x < n_pieces; ++round) {
       const int index = piece_index(round);
       if (index >= n_pieces) continue;
-      const Piece w = round == 0 ? first_piece : piece_of(p, index, n_qt);
+      const Piece w = piece_of(p, index, row_lo, n_rows);
       if (!w.valid) continue;
       for (int j = 0; ok && j < w.n_tiles; ++j) {
         const int c = j & 1, ord = (c ? had1 : had0) + j / 2;
@@ -342,7 +366,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     for (int round = 0; good && round * (int)gridDim.x < n_pieces; ++round) {
       const int index = piece_index(round);
       if (index >= n_pieces) continue;
-      const Piece pc = round == 0 ? first_piece : piece_of(p, index, n_qt);
+      const Piece pc = piece_of(p, index, row_lo, n_rows);
       if (!pc.valid) continue;
       const int n_tiles = pc.n_tiles, pos0 = pc.pos0, last_pos = pc.last_pos, kt_first = pc.kt_first, nq = pc.nq, t0 = pc.t0, h = pc.h;
       const int qpos = pos0 + r;
