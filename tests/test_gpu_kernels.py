@@ -441,6 +441,30 @@ def test_attention_decode_against_plain(G, KV, hd, ps, pages):
     assert_heads_close(out, refw, H, hd, "window")
 
 
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+def test_attention_prefill_among_many_single_tokens(kernel):
+    """A step of many single tokens (the decode kernel's) with the rows that bring several tokens in their midst:
+    the prefill kernels take exactly those rows, wherever they stand, and leave the others alone."""
+    o = ops()
+    H, KV, hd, ps = 8, 2, 128, 16
+    q_lens = [1] * 9 + [300] + [1] * 5 + [2] + [1] * 20 + [131] + [1] * 3
+    seq_lens = [50 + 7 * i for i in range(len(q_lens))]
+    for i, q in enumerate(q_lens):
+        seq_lens[i] = max(seq_lens[i], q)
+    case = PagedCase(torch.bfloat16, H, KV, hd, ps, seq_lens, q_lens, seed=5, scatter=True)
+    ref, _, _ = case.reference()
+    prefill = o.attention_prefill if kernel == "mma_sync" else o.attention_prefill_tc
+    err = o.new_error_record(DEV)
+    out = torch.full((case.T, H * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+    prefill(case.params(out, row_filter=2, err=err), max(q_lens))
+    o.raise_if_error(err)
+    starts = [sum(q_lens[:i]) for i in range(len(q_lens))]
+    single = torch.tensor([s for s, q in zip(starts, q_lens) if q == 1], device=DEV)
+    several = torch.tensor([s + j for s, q in zip(starts, q_lens) if q > 1 for j in range(q)], device=DEV)
+    assert bool((out[single] == 9.0).all()), "a single token's output was written"
+    assert_heads_close(out[several], ref[several.cpu()], H, hd, kernel)
+
+
 @pytest.mark.parametrize("pages", ["scattered, told so", "runs"])
 @pytest.mark.parametrize("G, KV, hd, ps", [(8, 4, 128, 16), (1, 3, 64, 8), (16, 1, 128, 64), (5, 2, 64, 32)])
 def test_attention_decode_splits_merged_by_a_cluster(G, KV, hd, ps, pages):
