@@ -56,3 +56,32 @@ def test_real_widths_fast_kernels_against_plain_kernels(monkeypatch):
     steps, ends = helpers.mixed(lengths, [n // 2 for n in lengths], seed=5)
     res = helpers.run_schedule(fast, toks, steps, ends)
     compare(res, refs, lengths, "real widths: mixed")
+
+
+def test_real_widths_against_the_plain_implementation(tmp_path):
+    """The same widths against the plain implementation on the CPU (short requests, so that it stays a matter of
+    seconds).  At a width of 4,096 and sums over 11,008 the rounding to bfloat16 itself moves the logits by 1.6 % of
+    the largest one (plain implementation in bfloat16 against itself in 32 bit), more than the 1 % that bounds the
+    tiny models; the bound here is that measured size of the rounding: the engine may differ from the plain
+    implementation in bfloat16 by no more than bfloat16 differs from 32 bit (1.2 % is what it does differ by).
+    A fault of the cache or of a kernel at these grids moves logits by many times that."""
+    from plain_yi import PlainYi
+    from delta_b200.config import EngineConfig
+    from delta_b200.engine.step import ModelRunner
+    from delta_b200.weights import write_random_model
+    import delta_b200.models  # noqa: F401
+    folder = write_random_model(tmp_path / "real_widths", CFG, 3, torch.bfloat16)
+    lengths = [150, 40]
+    toks = [helpers.random_tokens(n, CFG["vocab_size"], 500 + i) for i, n in enumerate(lengths)]
+    refs = [PlainYi(folder, rounding="bfloat16").forward(t) for t in toks]
+    exact = [PlainYi(folder).forward(t) for t in toks]
+    bounds = [(a - b).abs().max().item() for a, b in zip(refs, exact)]
+    assert all(0.005 * b.abs().max().item() < bound < 0.03 * b.abs().max().item() for bound, b in zip(bounds, exact)), bounds
+    r = ModelRunner(folder, engine_config=EngineConfig(max_batch=4, max_seq_len=256, page_size=16, dtype="bfloat16"))
+    for what, sched in (("whole", helpers.whole(lengths)), ("last 12 one by one", helpers.last_one_by_one(lengths, tail=12)),
+                        ("changing portions", helpers.changing_portions(lengths, seed=1))):
+        res = helpers.run_schedule(r, toks, sched)
+        for i, n in enumerate(lengths):
+            err = (helpers.stack_positions(res, i, n) - refs[i]).abs().amax(dim=-1)
+            assert err.max().item() <= bounds[i], (f"real widths, {what}: request {i} position {int(err.argmax())} differs by "
+                                                   f"{err.max().item():.4f}, the rounding's own size is {bounds[i]:.4f}")
