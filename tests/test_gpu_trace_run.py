@@ -89,8 +89,8 @@ def schedules(lengths, prompt_lens):
             "portions": (portions, ends_of(portions)), "mixed": (mixed, mixed_ends)}
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_with_the_selective_cache(model_folders, tmp_path, dtype):
+@pytest.mark.parametrize("dtype, ahead", [("float32", False), ("bfloat16", False), ("float32", True)])
+def test_trace_run_with_the_selective_cache(model_folders, tmp_path, dtype, ahead):
     """Configuration B with full_cache_layers=[1] and 4 pages through the program itself, in the four
     ways of cutting: logits and the pages each planner chose against the plain implementation.  The
     mixed replay runs with so few pages that they are used again, handed out in a shuffled order."""
@@ -99,14 +99,16 @@ def test_trace_run_with_the_selective_cache(model_folders, tmp_path, dtype):
     V = plain.cfg.vocab
     lengths, prompt_lens = [60, 100, 45, 130, 80], [9, 40, 20, 35, 1]
     toks = [helpers.random_tokens(n, V, 160 + i) for i, n in enumerate(lengths)]
-    sel = [Selective([1], k, 8, 1.0, ps, pl) for pl in prompt_lens]
+    # ``ahead``: pages counted as the reference's scheduler counts them (--count_page_ahead); the empty page it adds
+    # can be among the chosen, nothing is read from it, and the program leaves it out of what it writes
+    sel = [Selective([1], k, 8, 1.0, ps, pl, trailing_empty_page=ahead) for pl in prompt_lens]
     refs, want_pages = [], {}
     for i, t in enumerate(toks):
         refs.append(plain.forward(t, sel[i]))
-        want_pages.update({(i, l, p): pg for (l, p), pg in plain.last_planned.items()})
+        want_pages.update({(i, l, p): [j for j in pg if j * ps <= p] for (l, p), pg in plain.last_planned.items()})
     assert want_pages
     opts = ["--enable_selective_cache", "--full_cache_layers", 1, "--subset_cache_size", k, "--L", 8, "--page-size", ps,
-            "--dump-selected"]
+            "--dump-selected"] + (["--count_page_ahead"] if ahead else [])
     for name, (steps, ends) in schedules(lengths, prompt_lens).items():
         steps_json = []
         for n, (step, end) in enumerate(zip(steps, ends)):
