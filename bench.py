@@ -40,6 +40,8 @@ Other workloads (``--workload``), each printing one JSON line of the same shape:
   yi34b-mixed  Yi-34B shape: steps of one 2,048-token prompt portion beside up to 63 decoding
                requests; milliseconds per mixed step, tokens per second of both kinds, and the
                portion's share of the tensor-core peak
+  long-prompt  Yi-6B shape, one prompt of 30,000 tokens (``--context``) in portions of 2,048: milliseconds of the
+               first and the last portion, of the whole prompt, and of a decode step behind it
   grown        Yi-6B shape, 64 requests (``--batch``) of 64 + 2,400 tokens: nearly every page is taken
                during decoding, a page at a time in turns with the other requests; the last sixth of
                the decode steps, with the pool handing pages out in runs and one by one
@@ -214,7 +216,7 @@ def other_workload(args) -> int:
     pk = peaks()
     gen = torch.Generator().manual_seed(1)
     name = args.workload
-    shape = {"baseline": "yi-6b", "yi9b-long": "yi-9b", "yi34b-mixed": "yi-34b", "grown": "yi-6b"}[name]
+    shape = {"baseline": "yi-6b", "yi9b-long": "yi-9b", "yi34b-mixed": "yi-34b", "grown": "yi-6b", "long-prompt": "yi-6b"}[name]
     shape_name, shape_cfg = SHAPES[shape]
     layers = args.layers or shape_cfg["num_hidden_layers"]
     cfg = dict(shape_cfg, num_hidden_layers=layers)
@@ -283,6 +285,33 @@ def other_workload(args) -> int:
                                       generated=new, full_cache_layers="2", subset_cache_size=64, cuda_graph_decode=not args.no_graph),
                "full_cache": res["full"], "delta": res["delta"],
                "delta_over_full": res["delta"]["tokens_per_s"] / res["full"]["tokens_per_s"], "clocks": clk}
+    elif name == "long-prompt":
+        # One prompt of 30,000 tokens (--context sets another length) in portions of 2,048, then 16 decoded tokens: the
+        # portions' attention reads what the portions before left in the cache, so the later ones are bound by it.
+        plen = args.context if args.context != 4096 else 30000
+        cfg = dict(cfg, max_position_embeddings=max(cfg.get("max_position_embeddings", 0), plen + 64))
+        eng = engine(2, plen + 64, max_tokens_per_step=2048)
+        clocks.start()
+        for _ in range(2):              # the second run is the measured one (kernels chosen, buffers made)
+            records, _ = None, None
+            eng.step_timings.clear()
+            eng.record_timings = True
+            eng.add_requests(prompts(1, plen), [plen + 16], [], max_new_tokens=16)
+            eng.run_scheduler_loop()
+            eng.record_timings = False
+            records = list(eng.step_timings)
+        clk = clocks.stop()
+        pre = [r["model_forward_ms"] + r["postprocess_ms"] for r in records if r["tokens"] > 1]
+        dec = [r["model_forward_ms"] + r["postprocess_ms"] for r in records if r["tokens"] == 1]
+        flops = prefill_flops(plen)
+        out = {"workload": name, "metric": f"prefill tok/s ({shape_name}, bf16, one prompt of {plen} tokens in portions of 2,048)",
+               "value": plen / (sum(pre) / 1e3), "unit": "tokens/s", "n_gpus": 1, "ms_per_step": sum(pre) / len(pre), "higher_is_better": True,
+               "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids)",
+               "config": _flat_config(shape_name, shape_cfg, layers, global_batch=1, seq_len=plen, portion=2048, peaks=pk["source"]),
+               "prompt_ms": sum(pre), "first_portion_ms": pre[0], "last_full_portion_ms": pre[-2] if len(pre) > 1 else pre[-1],
+               "decode_ms_per_step_at_the_end": sum(dec) / max(1, len(dec)),
+               "prefill": {"value": plen / (sum(pre) / 1e3), "tokens": plen, "ms": sum(pre), "frac": flops / (sum(pre) / 1e3) / (pk["bf16_tflops"] * 1e12)},
+               "clocks": clk}
     elif name == "grown":
         # Many requests with short prompts that decode for a long time, in turns: nearly every page of a request
         # is taken during decoding, one at a time, between the pages the other requests take.  Measured with the
@@ -360,7 +389,7 @@ def main() -> int:
     ap.add_argument("--enable_selective_cache", action="store_true", help="DELTA on (not the default run)")
     ap.add_argument("--full_cache_layers", nargs="+", type=int, default=[0, 1, 2, 14, 22])
     ap.add_argument("--subset_cache_size", type=int, default=64)
-    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown"], default="decode")
+    ap.add_argument("--workload", choices=["decode", "baseline", "yi9b-long", "yi34b-mixed", "grown", "long-prompt"], default="decode")
     ap.add_argument("--generate", type=int, default=None, help="tokens generated per request in the other workloads (default: what the workload names)")
     args = ap.parse_args()
     if args.impl == "reference":
