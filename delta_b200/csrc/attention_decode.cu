@@ -623,10 +623,8 @@ __global__ void attention_decode_merge_kernel(const DkAttnParams p) {
 // lower (the attribute belongs to the device's copy of the kernel; setting it anew would also lower it).
 template <int HD, bool LOW, bool TMA>
 int configure(size_t smem) {
-  static size_t configured_on[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  size_t& configured = configured_on[dev & 63];
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, LOW, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {

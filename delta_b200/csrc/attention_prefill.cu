@@ -249,7 +249,8 @@ int launch(const DkAttnParams& pin, int max_q_len, cudaStream_t stream) {
     dk_set_error("attention_prefill: %d pages per request need more shared memory than a block has", p.max_pages);
     return DK_ERR_ARG;
   }
-  static size_t configured = 0;
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {

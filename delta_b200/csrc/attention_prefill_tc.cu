@@ -535,7 +535,8 @@ int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
                                          (unsigned long long)2 * p.KV * p.ps * HD * 2};
   DK_REQUIRE(make_tensor_map_bf16_4d(&map_run, p.kv, dims, strides, p.ps, KT / p.ps),
              "attention_prefill_tc: cannot encode the tensor map of runs of pages");
-  static bool configured = false;
+  static bool configured_on[DK_MAX_DEVICES] = {false};
+  bool& configured = configured_on[dk_current_device()];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) {
@@ -547,12 +548,7 @@ int launch(const DkAttnParams& p, int max_q_len, cudaStream_t stream) {
   const int n_qt = (max_q_len + QT - 1) / QT;
   const long long pieces = (long long)p.H * n_qt * p.rows;
   DK_REQUIRE(pieces < (1ll << 30), "attention_prefill_tc: too many pieces of work");
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
+  const int sms = dk_sm_count();
   static const bool one_each = getenv("DELTA_B200_PREFILL_ONE_PIECE_PER_BLOCK") != nullptr;   // for measurements: a block per piece
   const int blocks = (int)(one_each || pieces < sms ? pieces : sms);
   attention_prefill_tc_kernel<HD><<<blocks, THREADS, L::TOTAL, stream>>>(map_q, map_kv, map_run, p, n_qt);

@@ -27,6 +27,25 @@ void dk_set_error(const char* fmt, ...);
     }                                    \
   } while (0)
 
+// What a launcher has asked of a device (its number of SMs, the dynamic shared memory a kernel was granted there)
+// is kept per device: the answers of one device say nothing about another.
+constexpr int DK_MAX_DEVICES = 64;
+static inline int dk_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+  return dev % DK_MAX_DEVICES;
+}
+static inline int dk_sm_count() {
+  static int sms[DK_MAX_DEVICES] = {0};
+  const int dev = dk_current_device();
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
 static inline int dk_check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

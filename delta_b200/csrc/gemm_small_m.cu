@@ -206,12 +206,7 @@ void launch(const void* x, const void* W, void* out, int M, int N, int K, int ld
   if constexpr (SETS == 2) {
     GO_W(4);
   } else if constexpr (NT == 1) {
-    static int sms = 0;
-    if (sms == 0) {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = dk_sm_count();
     const int waves3 = (tiles + 3 * sms - 1) / (3 * sms), waves4 = (tiles + 4 * sms - 1) / (4 * sms);
     // (measured in the decode step of the Yi-6B shape, batch 8: 3.265 -> 3.227 ms with the deep instance for the
     // products of 256 blocks; held to three blocks per SM the compiler no longer keeps the loads in flight and nothing is gained)

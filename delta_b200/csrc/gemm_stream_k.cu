@@ -368,15 +368,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_stream_k_kernel(const __gr
 
 namespace {
 constexpr int FLAG_BYTES = 4096;   // head of the workspace: launch number, blocks done, one flag per block
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
+int sm_count() { return dk_sm_count(); }
 }  // namespace
 
 extern "C" int dk_gemm_stream_k_supported(int M, int N, int K, int swiglu) {
@@ -439,7 +431,8 @@ extern "C" int dk_gemm_stream_k(const void* x, const void* W, void* out, int M, 
   CUtensorMap map_w, map_x;
   DK_REQUIRE(make_tensor_map_bf16(&map_w, W, N, K, ldw, swiglu ? 64 : TILE_ROWS), "gemm_stream_k: cannot encode the tensor map of W");
   DK_REQUIRE(make_tensor_map_bf16(&map_x, x, M, K, lda, a.mpad), "gemm_stream_k: cannot encode the tensor map of x");
-  static size_t configured = 0;
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_stream_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {

@@ -281,7 +281,8 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   CUtensorMap map_w, map_x;
   DK_REQUIRE(make_map(&map_w, W, N, K, ldw, swiglu ? 64 : TILE_ROWS), "gemm_tc: cannot encode the tensor map of W");
   DK_REQUIRE(make_map(&map_x, x, M, K, lda, a.mpad), "gemm_tc: cannot encode the tensor map of x");
-  static size_t configured = 0;
+  static size_t configured_on[DK_MAX_DEVICES] = {0};
+  size_t& configured = configured_on[dk_current_device()];
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
