@@ -86,6 +86,28 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
+  // one step of the ring: the boxes of W and of x for step i into stage i % stages
+  auto request = [&](int i) {
+    const int s = i % a.stages;
+    const uint32_t dst0 = s2u(smem + (size_t)s * stage_bytes);
+    mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
+    for (int sub = 0; sub < KSUB; ++sub) {
+      const int kc = ((ks_begin + i) * KSUB + sub) * KSTEP;     // past K the boxes are filled with zeros
+      const uint32_t dst = dst0 + sub * a_bytes;
+      if (a.swiglu) {
+        tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);                           // 64 gate rows
+        tma_load_2d(dst + 64 * KSTEP * 2, &map_w, kc, a.n_up + n0, full0 + 8 * s);  // their 64 up rows
+      } else {
+        tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);
+      }
+      tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, 0, full0 + 8 * s);
+    }
+  };
+  // The first round of the ring needs nothing but the barriers this thread has just made: it is asked for
+  // before the block meets, so that the memory is already at work while the tensor memory is handed out.
+  const int ahead = min(n_steps, a.stages);
+  if (tid == 0)
+    for (int i = 0; i < ahead; ++i) request(i);
   if (warp == 1) {   // one warp allocates the tensor memory for the accumulator
     tmem_alloc(s2u(&tmem_base_slot), a.tmem_cols);
   }
@@ -96,25 +118,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
   if (tid == 0) {
     // producer
-    for (int i = 0; i < n_steps; ++i) {
+    for (int i = ahead; i < n_steps; ++i) {
       const int s = i % a.stages;
-      if (i >= a.stages && !mbar_wait(empty0 + 8 * s, ((i / a.stages) - 1) & 1)) {
+      if (!mbar_wait(empty0 + 8 * s, ((i / a.stages) - 1) & 1)) {
         failed = 1;
         break;
       }
-      const uint32_t dst0 = s2u(smem + (size_t)s * stage_bytes);
-      mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
-      for (int sub = 0; sub < KSUB; ++sub) {
-        const int kc = ((ks_begin + i) * KSUB + sub) * KSTEP;     // past K the boxes are filled with zeros
-        const uint32_t dst = dst0 + sub * a_bytes;
-        if (a.swiglu) {
-          tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);                           // 64 gate rows
-          tma_load_2d(dst + 64 * KSTEP * 2, &map_w, kc, a.n_up + n0, full0 + 8 * s);  // their 64 up rows
-        } else {
-          tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);
-        }
-        tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, 0, full0 + 8 * s);
-      }
+      request(i);
     }
   } else if (tid == 32) {
     // MMA issuer
