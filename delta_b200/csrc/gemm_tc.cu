@@ -1,6 +1,7 @@
 // y[M,N] = x[M,K] W[N,K]^T on the fifth-generation tensor cores, for decode steps (M up to
 // 128 rows): the weights stream once through shared memory by TMA and never touch
-// registers.
+// registers.  More rows (prompt portions) are taken in chunks of up to 256 by one block per
+// (tile of W, chunk), as a measure of what the library's product is worth there.
 //
 // "Swap AB": a block owns 128 rows of W, which are the M side of a tcgen05.mma tile
 // (A operand), and all M activation rows, padded to a multiple of 16, are its N side (B
@@ -47,7 +48,8 @@ struct TcArgs {
   int swiglu;        // rows of the tile: 64 gate rows then the 64 up rows that belong to them
   int n_up;          // first up row in W (= columns of the output) when swiglu
   int tmem_cols;
-  int ksub;          // boxes of 64 elements of K per stage (4, or 2 when many rows leave less room)
+  int ksub;          // boxes of 64 elements of K per stage (4, or 2 or 1 when many rows leave less room)
+  int chunks;        // groups of mpad rows of x: block (tile, chunk) makes rows [chunk * mpad, ...) of the tile's columns
 };
 
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -66,7 +68,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   cg::cluster_group cluster = cg::this_cluster();
   const int splits = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
-  const int tile = blockIdx.x;                       // 128 rows of W (64 + 64 with the SwiGLU epilogue)
+  // 128 rows of W (64 + 64 with the SwiGLU epilogue).  The chunks of one tile are neighbours in the grid, so that
+  // a tile of W is fetched from memory once and then found in the L2 by the blocks of the other chunks.
+  const int tile = blockIdx.x / a.chunks;
+  const int m0 = (blockIdx.x % a.chunks) * a.mpad;    // first row of x and of the output of this block
+  const int m_here = min(a.mpad, a.M - m0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rows_out = a.swiglu ? 64 : TILE_ROWS;    // output columns this tile makes
   const int n0 = tile * rows_out;
@@ -100,7 +106,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
       } else {
         tma_load_2d(dst, &map_w, kc, n0, full0 + 8 * s);
       }
-      tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, 0, full0 + 8 * s);
+      tma_load_2d(dst0 + KSUB * a_bytes + sub * b_bytes, &map_x, kc, m0, full0 + 8 * s);   // rows past M are zeros
     }
   };
   // The first round of the ring needs nothing but the barriers this thread has just made: it is asked for
@@ -183,7 +189,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   const float* parts[8];
 #pragma unroll
   for (int b = 0; b < 8; ++b) parts[b] = (b < splits && splits > 1) ? cluster.map_shared_rank(part, b) : part;
-  for (int item = tid; item < groups * a.M; item += TC_THREADS) {
+  for (int item = tid; item < groups * m_here; item += TC_THREADS) {
     const int m = item / groups, r = r_begin + (item % groups) * 8;
     float4 g0[8], g1[8], u0[8], u1[8];
 #pragma unroll
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         for (int i = 0; i < 8; ++i) y[i] = y[i] / (1.f + expf(-y[i])) * u[i];
       }
       if (a.out_f32) {
-        float* dst = (float*)a.out + (size_t)m * a.ldc + n;
+        float* dst = (float*)a.out + (size_t)(m0 + m) * a.ldc + n;
         *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
         *reinterpret_cast<float4*>(dst + 4) = make_float4(y[4], y[5], y[6], y[7]);
       } else {
@@ -228,7 +234,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         st.y = *reinterpret_cast<uint32_t*>(&p1);
         st.z = *reinterpret_cast<uint32_t*>(&p2);
         st.w = *reinterpret_cast<uint32_t*>(&p3);
-        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + (size_t)m * a.ldc + n) = st;
+        *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + (size_t)(m0 + m) * a.ldc + n) = st;
       }
     }
   }
@@ -253,6 +259,13 @@ extern "C" int dk_gemm_tc_supported(int M, int N, int K, int swiglu) {
   return 1;
 }
 
+// More than 128 rows (prompt portions): the same kernel with the rows of x in chunks of up to 256, one block per
+// (tile of W, chunk); K is not split and a block has the SM to itself.
+extern "C" int dk_gemm_tc_many_rows_supported(int M, int N, int K, int swiglu) {
+  if (M <= 128 || M > (1 << 20)) return 0;
+  return dk_gemm_tc_supported(128, N, K, swiglu);
+}
+
 // splits: blocks that share K as one cluster (1, 2, 4 or 8).  out_dtype DK_BF16 or DK_F32.
 // per_sm: 1, or 2 to size the ring of stages so that two blocks share an SM's shared memory (stages of half the
 // length): with more tiles than SMs but no more than twice as many (11,008 SwiGLU columns are 172 tiles), all
@@ -260,7 +273,10 @@ extern "C" int dk_gemm_tc_supported(int M, int N, int K, int swiglu) {
 extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int lda, int ldw, int ldc,
                           int out_dtype, int swiglu, int splits, int per_sm, int* err, cudaStream_t stream) {
   DK_REQUIRE(per_sm == 1 || per_sm == 2, "gemm_tc: per_sm must be 1 or 2, got %d", per_sm);
-  DK_REQUIRE(dk_gemm_tc_supported(M, N, K, swiglu), "gemm_tc: sizes not taken: M=%d N=%d K=%d swiglu=%d", M, N, K, swiglu);
+  const bool many = M > 128;
+  DK_REQUIRE(many ? dk_gemm_tc_many_rows_supported(M, N, K, swiglu) : dk_gemm_tc_supported(M, N, K, swiglu),
+             "gemm_tc: sizes not taken: M=%d N=%d K=%d swiglu=%d", M, N, K, swiglu);
+  DK_REQUIRE(!many || (splits == 1 && per_sm == 1), "gemm_tc: more than 128 rows go with splits=1 and per_sm=1 (got %d, %d)", splits, per_sm);
   DK_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: splits must be 1, 2, 4 or 8, got %d", splits);
   DK_REQUIRE((lda % 8) == 0 && (ldw % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0,
              "gemm_tc: operands must start on 16-byte boundaries with leading sizes that are multiples of 8");
@@ -271,14 +287,15 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   a.out = out;
   a.err = err;
   a.M = M; a.N = N; a.K = K; a.ldc = ldc;
-  a.mpad = (M + 15) / 16 * 16;
+  a.mpad = M > 256 ? 256 : (M + 15) / 16 * 16;
+  a.chunks = (M + a.mpad - 1) / a.mpad;
   a.out_f32 = out_dtype == DK_F32;
   a.swiglu = swiglu;
   a.n_up = swiglu ? N / 2 : 0;
-  a.tmem_cols = a.mpad <= 32 ? 32 : (a.mpad <= 64 ? 64 : 128);
+  a.tmem_cols = a.mpad <= 32 ? 32 : (a.mpad <= 64 ? 64 : (a.mpad <= 128 ? 128 : 256));
   const int a_bytes = TILE_ROWS * KSTEP * 2;
   const int b_bytes = a.mpad * KSTEP * 2;
-  a.ksub = per_sm == 2 ? 2 : (a.mpad <= 64 ? KSUB_MAX : 2);
+  a.ksub = per_sm == 2 ? 2 : (a.mpad <= 64 ? KSUB_MAX : (a.mpad <= 128 ? 2 : 1));
   const int stage_bytes = a.ksub * (a_bytes + b_bytes);
   const int part_bytes = a.mpad * TILE_ROWS * 4;
   int stages = ((224 * 1024) / per_sm - 2048) / stage_bytes;
@@ -305,7 +322,8 @@ extern "C" int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N,
   const int n_out = swiglu ? N / 2 : N;
   const int tiles = (n_out + rows_out - 1) / rows_out;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles, splits, 1);
+  DK_REQUIRE((long long)tiles * a.chunks < (1ll << 31), "gemm_tc: too many blocks");
+  cfg.gridDim = dim3(tiles * a.chunks, splits, 1);
   cfg.blockDim = dim3(TC_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;

@@ -59,6 +59,7 @@ _SIGNATURES = {
     "dk_gemm_small_m_supported": [I, I, I, I],
     "dk_gemm_tc": [P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "dk_gemm_tc_supported": [I, I, I, I],
+    "dk_gemm_tc_many_rows_supported": [I, I, I, I],
     "dk_gemm_stream_k_supported": [I, I, I, I],
     "dk_gemm_stream_k": [P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "dk_wait_check": [P, C.c_longlong, P],

@@ -309,11 +309,16 @@ def gemm_tc_supported(M, N, K, swiglu=False) -> bool:
     return bool(_l.load().dk_gemm_tc_supported(M, N, K, int(swiglu)))
 
 
+def gemm_tc_many_rows_supported(M, N, K, swiglu=False) -> bool:
+    return bool(_l.load().dk_gemm_tc_many_rows_supported(M, N, K, int(swiglu)))
+
+
 def gemm_tc(x, w, out, swiglu=False, splits=1, err=None, per_sm=1):
     """out = x @ w^T for up to 128 rows of bfloat16 x on the tcgen05 tensor cores; the weights
     stream through shared memory by TMA.  ``splits`` blocks (1, 2, 4, 8) share K as a cluster.
     ``swiglu``: w holds gate rows then up rows, out [M, N/2] = silu(x gate^T) * (x up^T).
-    ``per_sm`` 2: shorter stages, so that two blocks fit on an SM."""
+    ``per_sm`` 2: shorter stages, so that two blocks fit on an SM.
+    More than 128 rows are taken in chunks of up to 256 (``splits`` and ``per_sm`` 1)."""
     M, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if swiglu else N

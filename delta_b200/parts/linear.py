@@ -4,7 +4,9 @@
 reduced-precision matrix mode, no split over K).  bfloat16 activations go
 through the tensor cores.  For large batches (prompt portions) that is the
 library product the reference uses for its ``nn.Linear`` layers
-(DELTA/Engine/DELTA/model.py:369-370, 498-500).  For the few rows of a decode
+(DELTA/Engine/DELTA/model.py:369-370, 498-500), measured once per shape against
+the tcgen05 kernel of this package taking the rows in chunks (which has lost on
+every shape measured so far).  For the few rows of a decode
 step the product is a stream over the weights and four kernels compete: the
 warp-level MMA kernel that loads weights straight into fragments, the persistent
 tcgen05/TMA kernel that cuts the (tile, K step) sequence into one piece per SM,
@@ -22,8 +24,9 @@ import torch
 
 from ..kernels import ops
 
-SMALL_M = 128          # up to this many rows a product counts as weight streaming and is tuned
-_BUCKETS = (8, 16, 32, 64, 128)
+SMALL_M = 128          # up to this many rows a product counts as weight streaming
+MANY_M = 4096          # up to this many rows the library's product is measured against the tcgen05 kernel in chunks of rows
+_BUCKETS = (8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096)
 _choice: Dict[tuple, str] = {}
 _times: Dict[tuple, Dict[str, float]] = {}
 _flush: Optional[torch.Tensor] = None
@@ -52,6 +55,13 @@ def _bucket(m: int) -> int:
 
 def _candidates(m: int, n: int, k: int, swiglu: bool, out_dtype) -> List[str]:
     c = []
+    if m > SMALL_M:
+        # prompt portions: the library (what the reference uses) unless the kernel of this package beats it
+        if out_dtype == torch.bfloat16:
+            c.append("lib")
+        if ops.gemm_tc_many_rows_supported(m, n, k, swiglu):
+            c.append("tcr")
+        return c
     if m <= 64 and ops.gemm_small_m_supported(m, n, k, swiglu):
         c.append("small")
     if ops.gemm_tc_supported(m, n, k, swiglu):
@@ -74,6 +84,8 @@ def _run(kind: str, x, w, out, swiglu: bool, err=None):
         return ops.gemm_small_m(x, w, out, swiglu=swiglu)
     if kind == "sk":
         return ops.gemm_stream_k(x, w, out, swiglu=swiglu, err=err)
+    if kind == "tcr":
+        return ops.gemm_tc(x, w, out, swiglu=swiglu, err=err)
     if kind.startswith("tc"):
         two = kind.endswith("d")
         return ops.gemm_tc(x, w, out, swiglu=swiglu, splits=int(kind[2:3]), err=err, per_sm=2 if two else 1)
@@ -172,7 +184,7 @@ def load_choices(path) -> int:
     import json
     with open(path) as f:
         items = json.load(f)["product_kernels"]
-    known = {"small", "lib", "sk", "none", "tc1", "tc2", "tc4", "tc8", "tc1d", "tc2d"}
+    known = {"small", "lib", "sk", "none", "tc1", "tc2", "tc4", "tc8", "tc1d", "tc2d", "tcr"}
     for it in items:
         if it["kernel"] not in known:
             raise ValueError(f"{path}: unknown product kernel '{it['kernel']}'")
@@ -184,11 +196,11 @@ def swiglu_linear(ctx, x: torch.Tensor, w_gate_up: torch.Tensor):
     """silu(x gate^T) * (x up^T) with the gate fused into the product's epilogue when the batch
     is small enough for the streaming kernels; else None."""
     T = x.shape[0]
-    if x.dtype != torch.bfloat16 or ("products" in ctx.plain_kernels) or not (0 < T <= SMALL_M):
+    if x.dtype != torch.bfloat16 or ("products" in ctx.plain_kernels) or not (0 < T <= MANY_M):
         return None
     kind = choose(T, w_gate_up, x, True, x.dtype, ctx.err)
-    if kind == "none":
-        return None
+    if kind == "none" or (kind == "lib" and T > SMALL_M):
+        return None       # (the caller's library product and SwiGLU kernel)
     out = torch.empty((T, w_gate_up.shape[0] // 2), dtype=x.dtype, device=x.device)
     _run(kind, x, w_gate_up, out, True, ctx.err)
     return out
@@ -203,9 +215,9 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tenso
         if T:
             ops.gemm_nt_plain(x, w, out)
         return out
-    if 0 < T <= SMALL_M:
+    if 0 < T <= MANY_M:
         kind = choose(T, w, x, False, out_dtype, ctx.err)
-        if kind != "none":
+        if kind not in ("none", "lib") or (kind == "lib" and T <= SMALL_M):
             out = torch.empty((T, N), dtype=out_dtype, device=x.device)
             _run(kind, x, w, out, False, ctx.err)
             return out

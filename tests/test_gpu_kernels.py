@@ -233,6 +233,38 @@ def test_gemm_tc_swiglu(M, I, K, splits):
     assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [129, 200, 256, 257, 600, 2048])
+@pytest.mark.parametrize("N, K", [(128, 64), (1000, 344), (4096, 1024), (1408, 520)])
+def test_gemm_tc_many_rows(M, N, K):
+    """More than 128 rows in chunks of up to 256, one block per (tile, chunk): a chunk that is not
+    full, a last chunk of one row, and rows beyond the last that must stay untouched."""
+    o = ops()
+    torch.manual_seed(M + N)
+    err = o.new_error_record(DEV)
+    assert o.gemm_tc_many_rows_supported(M, N, K) and not o.gemm_tc_many_rows_supported(128, N, K)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    whole = torch.full((M + 3, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_tc(x, w, whole[:M], err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(whole[:M], ref, atol=1e-3, rtol=1e-4)
+    assert bool((whole[M:] == 9.0).all())
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x, w, out, err=err)
+    o.raise_if_error(err)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2)
+    with pytest.raises(o.KernelError, match="splits=1"):
+        o.gemm_tc(x, w, out, splits=2, err=err)
+    if N % 128 == 0:
+        I = N // 2
+        want = torch.nn.functional.silu(ref[:, :I]) * ref[:, I:]
+        act = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
+        o.gemm_tc(x, w, act, swiglu=True, err=err)
+        o.raise_if_error(err)
+        assert torch.allclose(act.float(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("M", [1, 8, 17, 64, 100, 128])
 @pytest.mark.parametrize("N, K", [(128, 64), (1000, 344), (4096, 4096), (1408, 11008), (2048, 520), (20000, 256)])
 def test_gemm_stream_k(M, N, K):
